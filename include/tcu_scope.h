@@ -1,0 +1,156 @@
+/*
+ * tcu_scope.h -- C ABI of the B200 (sm_100a) segmented / full reduce and
+ * inclusive-scan library for fp16 arrays.
+ *
+ * The reference project (c3sr/tcu_scope) has no FFI; its operator surface is
+ * a set of header-only kernel templates
+ *     compute_wmma_<op>_<variant><SEGMENT_SIZE, WARPS_PER_BLOCK, ...>
+ *         (const half* d_in, OUT* d_out, [half* partial_sums,] size_t num_segments)
+ * launched by one Google-Benchmark driver per variant.  Each entry point below
+ * names the kernels / drivers it stands in for.  Conventions shared by all of
+ * them, taken from those call sites:
+ *   - the caller owns every device buffer (the drivers cudaMalloc them,
+ *     src/reduction/seg_wmma_16n.cu:35-36); nothing here allocates or frees;
+ *   - segment j occupies in[j*segment_size, (j+1)*segment_size)
+ *     (src/reduction/seg_wmma_16n.cu:14-25);
+ *   - work is queued on the given stream and the call returns at once;
+ *   - the return value is a tcu_status; nothing throws, nothing resets the
+ *     device (the reference does both, src/utils/error.hpp:28-46).
+ * Pointers are plain device pointers (void*), streams are cudaStream_t passed
+ * as void*; there are no C++ or torch types in any signature.
+ */
+#ifndef TCU_SCOPE_H_
+#define TCU_SCOPE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TCU_OK              = 0,
+  TCU_ERR_INVALID_ARG = 1, /* null / misaligned pointer, size overflow                  */
+  TCU_ERR_UNSUPPORTED = 2, /* segment size not a power of two >= 16, unknown algo/type  */
+  TCU_ERR_CUDA        = 3, /* a CUDA runtime call failed (see cudaGetLastError)         */
+  TCU_ERR_TIMEOUT     = 4, /* a bounded device-side wait ran out (tcu_device_error)     */
+  TCU_ERR_WORKSPACE   = 5  /* workspace missing or smaller than tcu_workspace_bytes()   */
+} tcu_status;
+
+typedef enum {
+  TCU_ALGO_AUTO    = 0, /* the tensor-core kernel                                       */
+  TCU_ALGO_MMA     = 1, /* TMA ring + mma.sync m16n8k16 against ones / triangular ones  */
+  TCU_ALGO_SHUFFLE = 2  /* same pipeline, CUDA-core adds + warp shuffles: the ablation  */
+} tcu_algo;
+
+typedef enum { TCU_OUT_F16 = 0, TCU_OUT_F32 = 1 } tcu_out_type;
+
+typedef enum {
+  TCU_OP_SEGMENTED_REDUCE = 0,
+  TCU_OP_SEGMENTED_SCAN   = 1,
+  TCU_OP_FULL_REDUCE      = 2,
+  TCU_OP_FULL_SCAN        = 3
+} tcu_op;
+
+/* Input distributions of tcu_fill_f16 (bit-identical to the CPU oracle's). */
+typedef enum {
+  TCU_DIST_UNIFORM_PM1 = 0, /* uniform in [-1, 1)                                       */
+  TCU_DIST_UNIFORM_01  = 1, /* uniform in [0, 1)                                        */
+  TCU_DIST_SMALL_INT   = 2, /* integers -2..2 (every sum exact in any precision)        */
+  TCU_DIST_CONST_0P001 = 3  /* half(0.001f): the reference's fill,
+                               src/reduction/seg_wmma_16n.cu:38                          */
+} tcu_dist;
+
+/*
+ * Segmented sum reduction: out[j] = sum of segment j.
+ * Replaces compute_wmma_segmented_reduction_16n (src/reduction/kernel.cuh:80-125),
+ * ..._256n (:301-356) and ..._256n_block (:418-485) and their drivers
+ * CUDA_WMMA_SEGMENTED_REDUCTION_16N / _256N / _256N_BLOCK
+ * (src/reduction/seg_wmma_16n.cu:137-221, seg_wmma_256n.cu:149-229).
+ * segment_size: a power of two >= 16 (the sizes of the reference's dispatch
+ * table, seg_wmma_16n.cu:146-172).  d_out: num_segments floats or halves.
+ * A workspace is needed only when segment_size > 16384.
+ */
+int tcu_segmented_reduce_f16(const void* d_in, void* d_out, int out_type, size_t num_segments,
+                             size_t segment_size, int algo, void* d_workspace,
+                             size_t workspace_bytes, void* stream);
+
+/*
+ * Segmented inclusive prefix sum: out[j*S + i] = in[j*S] + ... + in[j*S + i].
+ * Replaces compute_wmma_segmented_prefixsum_16n (src/prefixsum/kernel.cuh:86-150),
+ * ..._256n (:441-506), ..._256n_block (:586-678) and their drivers
+ * CUDA_WMMA_SEGMENTED_PREFIXSUM_16N / _256N (src/prefixsum/seg_wmma_16n.cu:139-223,
+ * seg_wmma_256n.cu:143-222).  d_out: num_segments*segment_size halves or floats.
+ * A workspace is needed only when segment_size > 16384.
+ */
+int tcu_segmented_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_segments,
+                           size_t segment_size, int algo, void* d_workspace,
+                           size_t workspace_bytes, void* stream);
+
+/*
+ * Sum of all num_elements inputs (a multiple of 16) into *d_out (float) and,
+ * if d_out_f64 is not null, into *d_out_f64 (double; what a multi-GPU caller
+ * gathers).  Replaces CUDA_WMMA_FULL_REDUCTION_2KERS[_BLOCK]_BASE_{16,256}
+ * (src/reduction/wmma_2kers.cu:17-193): segmented kernel + cub::DeviceReduce.
+ * Always needs a workspace.
+ */
+int tcu_full_reduce_f16(const void* d_in, float* d_out, double* d_out_f64, size_t num_elements,
+                        int algo, void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Inclusive prefix sum over all num_elements inputs (a multiple of 16).
+ * Replaces CUDA_WMMA_FULL_PREFIXSUM_3KERS[_BLOCK] (src/prefixsum/wmma_3kers.cu:14-177):
+ * ..._256n_ps + cub::DeviceScan::ExclusiveSum + add_partial_sums, here one pass.
+ * For a scan sharded over several GPUs, d_shard_totals points at the gathered
+ * per-shard totals (device memory, doubles) and shard_index is this GPU's
+ * position: the sum of the earlier shards' totals seeds the scan.  Pass NULL
+ * and 0 on one GPU.  Always needs a workspace.
+ */
+int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                      const double* d_shard_totals, int shard_index, int algo,
+                      void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of device workspace the operation needs (0 = none).  The workspace
+ * needs no initialisation; one workspace must not be shared by calls that can
+ * run at the same time. */
+size_t tcu_workspace_bytes(int op, size_t num_elements, size_t segment_size);
+
+/*
+ * Seeded input fill, element i = f(seed, first_index + i): the build's
+ * replacement for cuda_memory_set / setFP16 (src/utils/cuda_helpers.cuh:123-181).
+ * Shards of one logical array are filled independently by passing their
+ * first global index.  n must be a multiple of 8.
+ */
+int tcu_fill_f16(void* d_out, size_t n, uint64_t seed, uint64_t first_index, int dist,
+                 void* stream);
+
+/*
+ * Same operations with HOST buffers: input is copied to the device in chunks
+ * of whole segments that overlap with the kernels, results are copied back.
+ * h_in / h_out should be pinned for full copy bandwidth.  The context owns
+ * its staging buffers and streams (created once; this is the only place the
+ * library allocates).  op selects the operation; for the full operations
+ * segment_size is ignored.  The call returns when h_out is complete.
+ */
+typedef struct tcu_host_ctx tcu_host_ctx;
+int tcu_host_ctx_create(tcu_host_ctx** ctx, size_t chunk_elements);
+void tcu_host_ctx_destroy(tcu_host_ctx* ctx);
+int tcu_host_run_f16(tcu_host_ctx* ctx, int op, const void* h_in, void* h_out, int out_type,
+                     size_t num_elements, size_t segment_size, int algo);
+
+/* Reads (and optionally clears) the device-side error word of the current
+ * device: bit 0 = an mbarrier wait ran out, bit 1 = a tile-status poll ran
+ * out.  Synchronises the device.  Returns TCU_ERR_TIMEOUT if any bit is set. */
+int tcu_device_error(unsigned int* bits, int clear);
+
+/* Geometry the kernels were built with, for callers that size experiments. */
+int tcu_tile_elements(void);
+int tcu_num_sms(void);
+
+const char* tcu_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCU_SCOPE_H_ */

@@ -1,0 +1,350 @@
+// C ABI of the library (see include/tcu_scope.h): argument validation, the
+// runtime -> compile-time dispatch on segment size that the reference does
+// with a switch over template instantiations
+// (src/reduction/seg_wmma_16n.cu:137-172), workspace layout and launches.
+// Nothing in this file allocates device memory.
+#include "../../include/tcu_scope.h"
+
+#include <cuda_runtime.h>
+
+#include <new>
+
+#include "common.cuh"
+#include "fill_kernels.cuh"
+#include "reduce_kernels.cuh"
+#include "scan_kernels.cuh"
+#include "scan_lookback_kernel.cuh"
+#include "shuffle_kernels.cuh"
+
+namespace {
+
+using namespace tcu;
+
+constexpr int kMaxDevices    = 64;
+constexpr size_t kWsHeader   = 256;   // counters live in the first 256 bytes
+constexpr int kMaxLongGrid   = 1024;  // boundary records must fit the idle ring
+constexpr int kDynSmemBytes  = kRingBytes + 128;
+
+int g_sm_count[kMaxDevices];
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  return (dev >= 0 && dev < kMaxDevices) ? dev : -1;
+}
+
+int sm_count() {
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+// log2 of a power-of-two segment size >= 16, folded into the kernel classes;
+// -1 for anything else.
+int segment_class(size_t s) {
+  if (s < 16 || (s & (s - 1)) != 0) return -1;
+  int l = 0;
+  while ((size_t(1) << l) < s) ++l;
+  return l <= 14 ? l : kClassLong;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool mul_overflows(size_t a, size_t b, size_t* out) {
+  if (a != 0 && b > (SIZE_MAX / 2) / a) return true;  // also keeps 2*a*b representable
+  *out = a * b;
+  return false;
+}
+
+template <typename K>
+cudaError_t ensure_smem(K kernel, bool* configured, int bytes) {
+  const int dev = current_device();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    const cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  return cudaSuccess;
+}
+
+template <int SC>
+cudaError_t launch_reduce(const ReduceParams& p, int grid, cudaStream_t st) {
+  static bool configured[kMaxDevices];
+  cudaError_t e = ensure_smem(seg_reduce_kernel<SC, true>, configured, kDynSmemBytes);
+  if (e != cudaSuccess) return e;
+  seg_reduce_kernel<SC, true><<<grid, kThreads, kDynSmemBytes, st>>>(p);
+  return cudaGetLastError();
+}
+
+template <int SC, bool OUT32>
+cudaError_t launch_scan(const ScanParams& p, int grid, cudaStream_t st) {
+  static bool configured[kMaxDevices];
+  cudaError_t e = ensure_smem(seg_scan_kernel<SC, OUT32>, configured, kDynSmemBytes);
+  if (e != cudaSuccess) return e;
+  seg_scan_kernel<SC, OUT32><<<grid, kThreads, kDynSmemBytes, st>>>(p);
+  return cudaGetLastError();
+}
+
+template <bool OUT32>
+cudaError_t launch_scan_lookback(const ScanParams& p, int grid, cudaStream_t st) {
+  static bool configured[kMaxDevices];
+  cudaError_t e = ensure_smem(scan_lookback_kernel<OUT32>, configured, kLookbackDynSmemBytes);
+  if (e != cudaSuccess) return e;
+  scan_lookback_kernel<OUT32><<<grid, kThreads, kLookbackDynSmemBytes, st>>>(p);
+  return cudaGetLastError();
+}
+
+template <int SC>
+cudaError_t launch_shuffle_reduce(const ReduceParams& p, int grid, cudaStream_t st) {
+  static bool configured[kMaxDevices];
+  cudaError_t e = ensure_smem(seg_reduce_kernel<SC, false>, configured, kDynSmemBytes);
+  if (e != cudaSuccess) return e;
+  seg_reduce_kernel<SC, false><<<grid, kThreads, kDynSmemBytes, st>>>(p);
+  return cudaGetLastError();
+}
+
+template <int SC, bool OUT32>
+cudaError_t launch_shuffle_scan(const ScanParams& p, int grid, cudaStream_t st) {
+  static bool configured[kMaxDevices];
+  cudaError_t e = ensure_smem(shuffle_scan_kernel<SC, OUT32>, configured, kDynSmemBytes);
+  if (e != cudaSuccess) return e;
+  shuffle_scan_kernel<SC, OUT32><<<grid, kThreads, kDynSmemBytes, st>>>(p);
+  return cudaGetLastError();
+}
+
+#define TCU_FOR_SHORT_CLASSES(X) X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13) X(14)
+
+size_t reduce_long_ws_bytes() { return kWsHeader + size_t(2) * kMaxLongGrid * 16; }
+
+size_t scan_long_ws_bytes(size_t num_elements) {
+  const size_t tiles = (num_elements + kTileElems - 1) / kTileElems;
+  return kWsHeader + tiles * 8;
+}
+
+int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
+                size_t num_segments, size_t segment_size, int sc, int algo, void* ws,
+                size_t ws_bytes, cudaStream_t st) {
+  if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
+  if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE)
+    return TCU_ERR_UNSUPPORTED;
+  size_t n = 0;
+  if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
+  if (n == 0) return TCU_OK;
+  // short classes store vectors of outputs, the long class single values
+  const uintptr_t out_mask = sc == kClassLong ? 3u : 15u;
+  if (!d_in || !d_out || !aligned16(d_in) || (reinterpret_cast<uintptr_t>(d_out) & out_mask) != 0)
+    return TCU_ERR_INVALID_ARG;
+  if (d_out_f64 && (reinterpret_cast<uintptr_t>(d_out_f64) & 7u) != 0) return TCU_ERR_INVALID_ARG;
+  const int sms = sm_count();
+  if (sms <= 0) return TCU_ERR_CUDA;
+
+  ReduceParams p{};
+  p.in           = static_cast<const uint8_t*>(d_in);
+  p.out          = d_out;
+  p.num_elems    = n;
+  p.num_segments = num_segments;
+  p.out_is_f32   = out_type == TCU_OUT_F32;
+  p.out_f64      = d_out_f64;
+  const size_t tiles = (n + kTileElems - 1) / kTileElems;
+  int grid           = tiles < size_t(sms) ? int(tiles) : sms;
+
+  cudaError_t e = cudaSuccess;
+  if (sc == kClassLong) {
+    if (!ws || ws_bytes < reduce_long_ws_bytes() || !aligned16(ws)) return TCU_ERR_WORKSPACE;
+    if (grid > kMaxLongGrid) grid = kMaxLongGrid;
+    uint8_t* w          = static_cast<uint8_t*>(ws);
+    p.done_counter      = reinterpret_cast<unsigned int*>(w);
+    p.bound_val         = reinterpret_cast<double*>(w + kWsHeader);
+    p.bound_seg         = reinterpret_cast<long long*>(w + kWsHeader + size_t(2) * kMaxLongGrid * 8);
+    // one segment (the full reduction): any multiple of 16 elements, all tiles are segment 0
+    p.tiles_per_segment = num_segments == 1 ? tiles : segment_size / kTileElems;
+    if (cudaMemsetAsync(w, 0, kWsHeader, st) != cudaSuccess) return TCU_ERR_CUDA;
+    e = (algo == TCU_ALGO_SHUFFLE) ? launch_shuffle_reduce<kClassLong>(p, grid, st)
+                                   : launch_reduce<kClassLong>(p, grid, st);
+  } else if (algo == TCU_ALGO_SHUFFLE) {
+    switch (sc) {
+#define X(C) case C: e = launch_shuffle_reduce<C>(p, grid, st); break;
+      TCU_FOR_SHORT_CLASSES(X)
+#undef X
+      default: return TCU_ERR_UNSUPPORTED;
+    }
+  } else {
+    switch (sc) {
+#define X(C) case C: e = launch_reduce<C>(p, grid, st); break;
+      TCU_FOR_SHORT_CLASSES(X)
+#undef X
+      default: return TCU_ERR_UNSUPPORTED;
+    }
+  }
+  return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+}
+
+int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
+              size_t segment_size, int sc, const double* shard_totals, int shard_index, int algo,
+              void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
+  if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE)
+    return TCU_ERR_UNSUPPORTED;
+  size_t n = 0;
+  if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
+  if (n == 0) return TCU_OK;
+  if (!d_in || !d_out || !aligned16(d_in) || !aligned16(d_out)) return TCU_ERR_INVALID_ARG;
+  if (shard_index < 0 || (shard_index > 0 && !shard_totals)) return TCU_ERR_INVALID_ARG;
+  const int sms = sm_count();
+  if (sms <= 0) return TCU_ERR_CUDA;
+
+  ScanParams p{};
+  p.in         = static_cast<const uint8_t*>(d_in);
+  p.out        = d_out;
+  p.num_elems  = n;
+  p.out_is_f32 = out_type == TCU_OUT_F32;
+  const size_t tiles = (n + kTileElems - 1) / kTileElems;
+  const int grid     = tiles < size_t(sms) ? int(tiles) : sms;
+  const bool f32     = out_type == TCU_OUT_F32;
+
+  cudaError_t e = cudaSuccess;
+  if (sc == kClassLong) {
+    const size_t need = scan_long_ws_bytes(n);
+    if (!ws || ws_bytes < need || !aligned16(ws)) return TCU_ERR_WORKSPACE;
+    uint8_t* w          = static_cast<uint8_t*>(ws);
+    p.ticket            = reinterpret_cast<unsigned int*>(w);
+    p.tile_status       = reinterpret_cast<unsigned long long*>(w + kWsHeader);
+    p.tiles_per_segment = num_segments == 1 ? tiles : segment_size / kTileElems;
+    p.shard_totals      = shard_totals;
+    p.shard_index       = shard_index;
+    if (cudaMemsetAsync(w, 0, need, st) != cudaSuccess) return TCU_ERR_CUDA;
+    // two CTAs per SM: one hides the other's look-back latency
+    const size_t want = size_t(sms) * kLookbackCtasPerSm;
+    const int lgrid   = tiles < want ? int(tiles) : int(want);
+    if (algo == TCU_ALGO_SHUFFLE) return TCU_ERR_UNSUPPORTED;
+    e = f32 ? launch_scan_lookback<true>(p, lgrid, st) : launch_scan_lookback<false>(p, lgrid, st);
+  } else if (algo == TCU_ALGO_SHUFFLE) {
+    switch (sc) {
+#define X(C)                                                                         \
+  case C:                                                                            \
+    e = f32 ? launch_shuffle_scan<C, true>(p, grid, st) : launch_shuffle_scan<C, false>(p, grid, st); \
+    break;
+      TCU_FOR_SHORT_CLASSES(X)
+#undef X
+      default: return TCU_ERR_UNSUPPORTED;
+    }
+  } else {
+    switch (sc) {
+#define X(C)                                                                       \
+  case C:                                                                          \
+    e = f32 ? launch_scan<C, true>(p, grid, st) : launch_scan<C, false>(p, grid, st); \
+    break;
+      TCU_FOR_SHORT_CLASSES(X)
+#undef X
+      default: return TCU_ERR_UNSUPPORTED;
+    }
+  }
+  return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tcu_segmented_reduce_f16(const void* d_in, void* d_out, int out_type, size_t num_segments,
+                             size_t segment_size, int algo, void* d_workspace,
+                             size_t workspace_bytes, void* stream) {
+  const int sc = segment_class(segment_size);
+  if (sc < 0) return TCU_ERR_UNSUPPORTED;
+  return reduce_impl(d_in, d_out, nullptr, out_type, num_segments, segment_size, sc, algo,
+                     d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int tcu_segmented_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_segments,
+                           size_t segment_size, int algo, void* d_workspace,
+                           size_t workspace_bytes, void* stream) {
+  const int sc = segment_class(segment_size);
+  if (sc < 0) return TCU_ERR_UNSUPPORTED;
+  return scan_impl(d_in, d_out, out_type, num_segments, segment_size, sc, nullptr, 0, algo,
+                   d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+// The full operations are the long class with a single segment covering every
+// tile, so any multiple of 16 elements works, not just powers of two.
+int tcu_full_reduce_f16(const void* d_in, float* d_out, double* d_out_f64, size_t num_elements,
+                        int algo, void* d_workspace, size_t workspace_bytes, void* stream) {
+  // an empty sum has no element count to be a multiple of; reject it with the rest
+  if (num_elements == 0 || num_elements % 16 != 0) return TCU_ERR_INVALID_ARG;
+  return reduce_impl(d_in, d_out, d_out_f64, TCU_OUT_F32, 1, num_elements, kClassLong, algo,
+                     d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                      const double* d_shard_totals, int shard_index, int algo,
+                      void* d_workspace, size_t workspace_bytes, void* stream) {
+  if (num_elements % 16 != 0) return TCU_ERR_INVALID_ARG;
+  return scan_impl(d_in, d_out, out_type, 1, num_elements, kClassLong, d_shard_totals,
+                   shard_index, algo, d_workspace, workspace_bytes,
+                   static_cast<cudaStream_t>(stream));
+}
+
+size_t tcu_workspace_bytes(int op, size_t num_elements, size_t segment_size) {
+  switch (op) {
+    case TCU_OP_SEGMENTED_REDUCE:
+      return segment_size > size_t(kTileElems) ? reduce_long_ws_bytes() : 0;
+    case TCU_OP_FULL_REDUCE: return reduce_long_ws_bytes();
+    case TCU_OP_SEGMENTED_SCAN:
+      return segment_size > size_t(kTileElems) ? scan_long_ws_bytes(num_elements) : 0;
+    case TCU_OP_FULL_SCAN: return scan_long_ws_bytes(num_elements);
+    default: return 0;
+  }
+}
+
+int tcu_fill_f16(void* d_out, size_t n, uint64_t seed, uint64_t first_index, int dist,
+                 void* stream) {
+  if (n == 0) return TCU_OK;
+  if (!d_out || !aligned16(d_out) || n % 8 != 0) return TCU_ERR_INVALID_ARG;
+  if (dist < TCU_DIST_UNIFORM_PM1 || dist > TCU_DIST_CONST_0P001) return TCU_ERR_UNSUPPORTED;
+  const int sms = sm_count();
+  if (sms <= 0) return TCU_ERR_CUDA;
+  const size_t groups = n / 8;
+  const size_t want   = (groups + 255) / 256;
+  const int grid      = want < size_t(sms) * 16 ? int(want) : sms * 16;
+  fill_f16_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(d_out), groups, seed, first_index, dist);
+  return cudaGetLastError() == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+}
+
+int tcu_device_error(unsigned int* bits, int clear) {
+  unsigned int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return TCU_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(&v, g_error_word, sizeof(v)) != cudaSuccess) return TCU_ERR_CUDA;
+  if (clear && v) {
+    const unsigned int z = 0;
+    if (cudaMemcpyToSymbol(g_error_word, &z, sizeof(z)) != cudaSuccess) return TCU_ERR_CUDA;
+  }
+  if (bits) *bits = v;
+  return v ? TCU_ERR_TIMEOUT : TCU_OK;
+}
+
+int tcu_tile_elements(void) { return kTileElems; }
+
+int tcu_num_sms(void) { return sm_count(); }
+
+const char* tcu_status_string(int status) {
+  switch (status) {
+    case TCU_OK: return "ok";
+    case TCU_ERR_INVALID_ARG: return "invalid argument (null or misaligned pointer, bad size)";
+    case TCU_ERR_UNSUPPORTED: return "unsupported segment size, output type or algorithm";
+    case TCU_ERR_CUDA: return "CUDA runtime error";
+    case TCU_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case TCU_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    default: return "unknown status";
+  }
+}
+
+}  // extern "C"
+
+#include "host_pipeline.inl"

@@ -1,0 +1,150 @@
+// Shared device-side building blocks for the sm_100a reduce / scan kernels:
+// tile geometry, mbarrier + TMA bulk-copy wrappers with bounded waits, the
+// m16n8k16 tensor-core contraction and the constant operands it is fed.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tcu {
+
+// ---------------------------------------------------------------- geometry
+// One CTA tile is what a single TMA bulk copy brings into one ring stage.  A
+// tile is cut into one contiguous slice per consumer warp.
+constexpr int kTileElems     = 16384;               // halves per tile
+constexpr int kTileBytes     = kTileElems * 2;      // 32 KiB
+constexpr int kConsumerWarps = 8;
+constexpr int kSliceElems    = kTileElems / kConsumerWarps;  // 2048 halves
+constexpr int kSliceBytes    = kSliceElems * 2;              // 4 KiB
+constexpr int kStages        = 6;                            // 192 KiB ring
+constexpr int kThreads       = (kConsumerWarps + 1) * 32;    // + 1 producer warp
+constexpr int kRingBytes     = kStages * kTileBytes;
+
+// Device-side error word bits (read back by tcu_device_error()).
+constexpr unsigned kErrBarrierTimeout  = 1u;  // an mbarrier wait ran out
+constexpr unsigned kErrLookbackTimeout = 2u;  // a tile-status poll ran out
+
+// Wait bounds.  try_wait suspends for at most kWaitHintNs per attempt, so a
+// wait gives up after roughly kWaitAttempts * kWaitHintNs (about 2 s) instead
+// of hanging the device.
+constexpr uint32_t kWaitHintNs   = 1000;
+constexpr uint32_t kWaitAttempts = 1u << 21;
+constexpr uint32_t kPollAttempts = 1u << 22;  // tile-status polls (each ~0.5 us)
+
+__device__ unsigned int g_error_word;  // sticky until cleared by the host
+
+__device__ __forceinline__ void raise_error(unsigned bits) { atomicOr(&g_error_word, bits); }
+
+// ------------------------------------------------------------------ smem / mbarrier
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+// Bounded wait on a phase parity.  Returns false (after raising the error
+// word) when the phase never completed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t attempt = 0; attempt < kWaitAttempts; ++attempt) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
+        : "memory");
+    if (done) return true;
+  }
+  raise_error(kErrBarrierTimeout);
+  return false;
+}
+
+// Linear TMA: global -> this CTA's shared memory, completion counted in bytes
+// on an mbarrier.  Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src_gmem,
+                                            uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst_smem), "l"(src_gmem), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// Named barrier over the consumer warps only (the producer warp never joins).
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+}
+
+// ------------------------------------------------------------------ shared loads
+__device__ __forceinline__ uint4 lds128(const uint8_t* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+
+__device__ __forceinline__ uint2 lds64(const uint8_t* p) {
+  return *reinterpret_cast<const uint2*>(p);
+}
+
+// Zero the tail [valid_bytes, kSliceBytes) of one warp's slice.  Only the last
+// tile of an array can be short; stale shared memory behind it may hold NaN or
+// Inf bit patterns, and 0 * NaN inside the contraction would poison valid rows.
+__device__ __forceinline__ void zero_slice_tail(uint8_t* slice, int valid_bytes, int lane) {
+  for (int b = valid_bytes + lane * 16; b < kSliceBytes; b += 32 * 16)
+    *reinterpret_cast<uint4*>(slice + b) = make_uint4(0u, 0u, 0u, 0u);
+  __syncwarp();
+}
+
+// ------------------------------------------------------------------ tensor core
+// D(16x8,f32) = A(16x16,f16,row) * B(16x8,f16,col) + C.  Lane = 4*g + t holds
+//   A: a0={row g,  k 2t,2t+1}  a1={row g+8, k 2t,2t+1}
+//      a2={row g,  k 2t+8,+9}  a3={row g+8, k 2t+8,+9}
+//   B: b0={k 2t,2t+1; n g}     b1={k 2t+8,2t+9; n g}
+//   D: d0,d1={row g;   n 2t,2t+1}   d2,d3={row g+8; n 2t,2t+1}
+struct Acc {
+  float d0, d1, d2, d3;
+};
+
+__device__ __forceinline__ Acc mma16816(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1, Acc c) {
+  Acc d;
+  asm(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d.d0), "=f"(d.d1), "=f"(d.d2), "=f"(d.d3)
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c.d0), "f"(c.d1), "f"(c.d2),
+        "f"(c.d3));
+  return d;
+}
+
+constexpr uint32_t kOnesH2 = 0x3C003C00u;  // half2(1, 1)
+
+// x = hi + lo exactly, for every finite half x.  hi is x rounded to a multiple
+// of 2^-13 or coarser (the ulp of half in [0.25, 0.5) after adding 0.375), so
+// sums of up to 2^11 hi parts of inputs in [-1, 1] are exact in fp32; |lo| <=
+// 2^-11 and a multiple of 2^-24, so the same holds for the lo parts.  Feeding
+// the two parts to separate tensor-core accumulators makes every partial sum
+// exact, whatever order and rounding the hardware adder uses.
+__device__ __forceinline__ void split_hi_lo(uint32_t x, uint32_t& hi, uint32_t& lo) {
+  constexpr uint32_t kMagic = 0x36003600u;  // half2(0.375, 0.375)
+  uint32_t t;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(t) : "r"(x), "r"(kMagic));
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(t), "r"(kMagic));
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(x), "r"(hi));
+}
+
+}  // namespace tcu

@@ -1,0 +1,297 @@
+// Segmented and full inclusive prefix sum of fp16 arrays on the tensor cores.
+//
+// What it replaces in c3sr/tcu_scope: compute_wmma_segmented_prefixsum_16n
+// (src/prefixsum/kernel.cuh:86-150), ..._256n (:441-506), ..._256n_block
+// (:586-678) and the three-kernel full scan built on ..._256n_ps + a library
+// exclusive scan + add_partial_sums (src/prefixsum/wmma_3kers.cu:63-70).  The
+// contraction is the paper's: a 16 x 16 block of input rows times the
+// upper-triangular ones matrix U gives 16 independent 16-wide inclusive scans
+// (kernel.cuh:60,79-81).  Differences: one persistent single-pass kernel per
+// segment class, fp32 accumulation of exact hi/lo parts, the running carry fed
+// through the accumulator operand of the next MMA instead of a shared-memory
+// round trip, and a decoupled look-back chain across tiles in place of the
+// second and third kernel.
+//
+// Layout inside one warp's 4 KiB slice (2048 halves): 16 "rows" of 128
+// consecutive halves.  MMA row r walks row r of the slice 16 halves per step,
+// so the carry of a row flows from step to step inside that row (the C operand
+// of the next MMA), and only once per slice do the 16 row totals have to be
+// scanned across lanes with shuffles.  For 16-element segments there is no
+// carry at all and the rows are simply consecutive 16-element segments.
+#pragma once
+
+#include "common.cuh"
+
+namespace tcu {
+
+struct ScanParams {
+  const uint8_t* in;             // fp16 input, 16-byte aligned
+  void* out;                     // half or float per element, 16-byte aligned
+  unsigned long long num_elems;
+  int out_is_f32;
+  // look-back class only
+  unsigned long long tiles_per_segment;  // segment_size / kTileElems
+  unsigned long long* tile_status;       // [num_tiles], zeroed by the host before the launch
+  unsigned int* ticket;                  // dynamic tile counter, zeroed by the host
+  const double* shard_totals;            // optional: totals of all shards of a multi-GPU scan
+  int shard_index;                       // this GPU's position in shard_totals
+};
+
+// B operands for "A times U" with the k order that the 8-byte row loads give:
+// lane (g,t) holds row elements 4t..4t+3 as k = 2t, 2t+1, 2t+8, 2t+9.  Column
+// n of the first MMA is output position 4(n>>1) + (n&1), of the second one
+// that plus 2, so each lane ends up with the 4 consecutive outputs 4t..4t+3 of
+// its rows -- the same positions it loaded.
+struct ScanOperands {
+  uint32_t ua0, ua1, ub0, ub1;
+};
+
+__device__ __forceinline__ ScanOperands make_scan_operands(int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  const int qa = 4 * (g >> 1) + (g & 1), qb = qa + 2;
+  auto pack = [](bool e0, bool e1) -> uint32_t {
+    return (e0 ? 0x3C00u : 0u) | (e1 ? 0x3C000000u : 0u);
+  };
+  ScanOperands o;
+  o.ua0 = pack(4 * t + 0 <= qa, 4 * t + 1 <= qa);
+  o.ua1 = pack(4 * t + 2 <= qa, 4 * t + 3 <= qa);
+  o.ub0 = pack(4 * t + 0 <= qb, 4 * t + 1 <= qb);
+  o.ub1 = pack(4 * t + 2 <= qb, 4 * t + 3 <= qb);
+  return o;
+}
+
+template <bool OUT32>
+__device__ __forceinline__ void store4(void* out, unsigned long long idx, float r0, float r1,
+                                       float r2, float r3) {
+  if constexpr (OUT32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(out) + idx) = make_float4(r0, r1, r2, r3);
+  } else {
+    const __half2 a = __floats2half2_rn(r0, r1), b = __floats2half2_rn(r2, r3);
+    *reinterpret_cast<uint2*>(static_cast<__half*>(out) + idx) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+  }
+}
+
+// Byte offset inside the slice of the 8 bytes lane (g,t) loads for MMA row g
+// at step j (row g+8 is kHiOffset further).
+template <int SC>
+struct ScanGeom {
+  static constexpr bool kLinear   = SC == 4;
+  static constexpr int kHiOffset  = kLinear ? 256 : 2048;
+  __device__ static __forceinline__ int lo(int g, int t, int j) {
+    return kLinear ? 512 * j + 32 * g + 8 * t : 256 * g + 32 * j + 8 * t;
+  }
+};
+
+// Load the 2 x 8 bytes lane (g,t) owns at step j and split them into exact
+// hi / lo A operands: [0] row g k 2t,2t+1  [1] row g+8 k 2t,2t+1
+//                     [2] row g k 2t+8,+9  [3] row g+8 k 2t+8,+9.
+template <class Geom>
+__device__ __forceinline__ void load_split(const uint8_t* slice, int g, int t, int j,
+                                           uint32_t (&ah)[4], uint32_t (&al)[4]) {
+  const uint2 lo = lds64(slice + Geom::lo(g, t, j));
+  const uint2 hi = lds64(slice + Geom::lo(g, t, j) + Geom::kHiOffset);
+  split_hi_lo(lo.x, ah[0], al[0]);
+  split_hi_lo(hi.x, ah[1], al[1]);
+  split_hi_lo(lo.y, ah[2], al[2]);
+  split_hi_lo(hi.y, ah[3], al[3]);
+}
+
+__device__ __forceinline__ Acc mma_ones(const uint32_t (&a)[4], Acc c) {
+  return mma16816(a[0], a[1], a[2], a[3], kOnesH2, kOnesH2, c);
+}
+
+// Carry into each MMA row = sum of the totals of the earlier rows of the same
+// segment.  tot.d0 / tot.d2 hold the totals of rows g / g+8 (in every lane of
+// the group); slice rows are ordered 0..7 = "lo" rows of g = 0..7, 8..15 =
+// "hi" rows.  kRowsPerSeg in {2,4,8,16}.  Also returns the slice total (only
+// meaningful when all 16 rows form one segment).
+template <int kRowsPerSeg>
+__device__ __forceinline__ void row_carries(const Acc& tot_h, const Acc& tot_l, int g,
+                                            float& ch_lo, float& cl_lo, float& ch_hi,
+                                            float& cl_hi, float& slice_h, float& slice_l) {
+  constexpr int kRG = kRowsPerSeg >= 8 ? 8 : kRowsPerSeg;
+  float ih_lo = tot_h.d0, il_lo = tot_l.d0, ih_hi = tot_h.d2, il_hi = tot_l.d2;
+#pragma unroll
+  for (int d = 1; d < kRG; d <<= 1) {
+    const float a = __shfl_up_sync(0xffffffffu, ih_lo, 4 * d);
+    const float b = __shfl_up_sync(0xffffffffu, il_lo, 4 * d);
+    const float c = __shfl_up_sync(0xffffffffu, ih_hi, 4 * d);
+    const float e = __shfl_up_sync(0xffffffffu, il_hi, 4 * d);
+    if ((g & (kRG - 1)) >= d) {
+      ih_lo += a;
+      il_lo += b;
+      ih_hi += c;
+      il_hi += e;
+    }
+  }
+  ch_lo = __shfl_up_sync(0xffffffffu, ih_lo, 4);
+  cl_lo = __shfl_up_sync(0xffffffffu, il_lo, 4);
+  ch_hi = __shfl_up_sync(0xffffffffu, ih_hi, 4);
+  cl_hi = __shfl_up_sync(0xffffffffu, il_hi, 4);
+  if ((g & (kRG - 1)) == 0) ch_lo = cl_lo = ch_hi = cl_hi = 0.f;
+  slice_h = slice_l = 0.f;
+  if constexpr (kRowsPerSeg == 16) {
+    const float th = __shfl_sync(0xffffffffu, ih_lo, 28);  // total of rows 0..7
+    const float tl = __shfl_sync(0xffffffffu, il_lo, 28);
+    ch_hi += th;
+    cl_hi += tl;
+    slice_h = __shfl_sync(0xffffffffu, ih_hi, 28) + th;
+    slice_l = __shfl_sync(0xffffffffu, il_hi, 28) + tl;
+  }
+}
+
+// One step of one slice: 16 rows x 16 elements.  D = A.U + carry for the hi
+// and the lo parts (4 MMAs), the carry for the next step (2 more, only when a
+// segment continues), then out = hi + lo (+ the carry from earlier slices).
+template <int SC, bool OUT32, bool kExtraCarry>
+__device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                          const ScanOperands& ops, float& ch_lo, float& cl_lo,
+                                          float& ch_hi, float& cl_hi, float xh, float xl,
+                                          void* out, unsigned long long elem_base,
+                                          int valid_elems, int g, int t) {
+  using Geom = ScanGeom<SC>;
+  // a new segment starts inside the row at this step: drop the carry
+  if (SC == 4 || (SC == 5 && (j & 1) == 0) || (SC == 6 && (j & 3) == 0))
+    ch_lo = cl_lo = ch_hi = cl_hi = 0.f;
+  const Acc c_h{ch_lo, ch_lo, ch_hi, ch_hi}, c_l{cl_lo, cl_lo, cl_hi, cl_hi};
+  const Acc ha = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ua0, ops.ua1, c_h);
+  const Acc hb = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ub0, ops.ub1, c_h);
+  const Acc la = mma16816(al[0], al[1], al[2], al[3], ops.ua0, ops.ua1, c_l);
+  const Acc lb = mma16816(al[0], al[1], al[2], al[3], ops.ub0, ops.ub1, c_l);
+  const bool carry_on =
+      SC >= 7 ? (j != 7) : (SC == 6 ? (j & 3) != 3 : (SC == 5 && (j & 1) == 0));
+  if (carry_on) {
+    const Acc nh = mma_ones(ah, c_h), nl = mma_ones(al, c_l);
+    ch_lo = nh.d0;
+    ch_hi = nh.d2;
+    cl_lo = nl.d0;
+    cl_hi = nl.d2;
+  }
+  const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
+  if constexpr (kExtraCarry) {
+    if (e_lo < valid_elems)
+      store4<OUT32>(out, elem_base + e_lo, (ha.d0 + xh) + (la.d0 + xl), (ha.d1 + xh) + (la.d1 + xl),
+                    (hb.d0 + xh) + (lb.d0 + xl), (hb.d1 + xh) + (lb.d1 + xl));
+    if (e_hi < valid_elems)
+      store4<OUT32>(out, elem_base + e_hi, (ha.d2 + xh) + (la.d2 + xl), (ha.d3 + xh) + (la.d3 + xl),
+                    (hb.d2 + xh) + (lb.d2 + xl), (hb.d3 + xh) + (lb.d3 + xl));
+  } else {
+    if (e_lo < valid_elems)
+      store4<OUT32>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
+                    hb.d1 + lb.d1);
+    if (e_hi < valid_elems)
+      store4<OUT32>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
+                    hb.d3 + lb.d3);
+  }
+}
+
+// Segment classes as for the reduction: 4..11 = 2^class elements (inside one
+// slice), 12..14 = 4096/8192/16384 (2/4/8 slices of one tile).
+template <int SC, bool OUT32>
+__global__ void __launch_bounds__(kThreads, 1) seg_scan_kernel(const ScanParams p) {
+  static_assert(SC >= 4 && SC <= 14, "the look-back class has its own kernel");
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ __align__(8) uint64_t bars[2 * kStages];
+  __shared__ float2 part[2][kConsumerWarps];
+
+  uint8_t* ring = dyn_smem + ((128u - (smem_u32(dyn_smem) & 127u)) & 127u);
+  const uint32_t ring_u32 = smem_u32(ring);
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, kConsumerWarps);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const unsigned long long total_bytes = p.num_elems * 2ull;
+  const unsigned long long num_tiles   = (total_bytes + kTileBytes - 1) / kTileBytes;
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      uint32_t i = 0;
+      for (unsigned long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
+        const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) break;
+        const unsigned long long off = tile * kTileBytes;
+        const unsigned long long rem = total_bytes - off;
+        const uint32_t bytes = rem < (unsigned long long)kTileBytes ? (uint32_t)rem : kTileBytes;
+        mbar_arrive_expect_tx(full0 + 8 * s, bytes);
+        tma_load_1d(ring_u32 + s * kTileBytes, p.in + off, bytes, full0 + 8 * s);
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------- consumers
+  using Geom = ScanGeom<SC>;
+  const int g = lane >> 2, t = lane & 3;
+  const ScanOperands ops = make_scan_operands(lane);
+  const Acc zero{0.f, 0.f, 0.f, 0.f};
+  bool dead = false;
+
+  uint32_t i = 0;
+  for (unsigned long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
+    const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
+    if (!dead && !mbar_wait(full0 + 8 * s, ph)) dead = true;
+
+    uint8_t* slice = ring + s * kTileBytes + warp * kSliceBytes;
+    const unsigned long long slice_off = tile * kTileBytes + (unsigned long long)warp * kSliceBytes;
+    const long long left  = (long long)total_bytes - (long long)slice_off;
+    const int valid_bytes = left <= 0 ? 0 : (left < kSliceBytes ? (int)left : kSliceBytes);
+    const bool active     = !dead && valid_bytes > 0;
+    if (active && valid_bytes < kSliceBytes) zero_slice_tail(slice, valid_bytes, lane);
+
+    // ---- load + split the whole slice; row totals for classes that chain rows
+    uint32_t ah[8][4], al[8][4];
+    Acc tot_h = zero, tot_l = zero;
+    if (active) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        load_split<Geom>(slice, g, t, j, ah[j], al[j]);
+        if constexpr (SC >= 8) {
+          tot_h = mma_ones(ah[j], tot_h);
+          tot_l = mma_ones(al[j], tot_l);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8 * s);  // everything needed is in registers
+
+    // ---- carries into each MMA row, and from the earlier slices of the segment
+    float ch_lo = 0.f, cl_lo = 0.f, ch_hi = 0.f, cl_hi = 0.f;
+    float xh = 0.f, xl = 0.f;
+    if constexpr (SC >= 8) {
+      constexpr int kRowsPerSeg = SC >= 11 ? 16 : (1 << (SC - 7));
+      float slice_h, slice_l;
+      row_carries<kRowsPerSeg>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
+      if constexpr (SC >= 12) {
+        if (lane == 0)
+          part[i & 1][warp] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
+        consumer_sync();
+        constexpr int kWarpsPerSeg = 1 << (SC - 11);  // 2, 4, 8
+        const int w0 = warp & ~(kWarpsPerSeg - 1);
+        for (int w = w0; w < warp; ++w) {
+          const float2 pr = part[i & 1][w];
+          xh += pr.x;
+          xl += pr.y;
+        }
+      }
+    }
+    if (!active) continue;
+
+    const unsigned long long elem_base = slice_off / 2;
+    const int valid_elems = valid_bytes / 2;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      scan_step<SC, OUT32, (SC >= 12)>(j, ah[j], al[j], ops, ch_lo, cl_lo, ch_hi, cl_hi, xh, xl,
+                                       p.out, elem_base, valid_elems, g, t);
+  }
+}
+
+}  // namespace tcu

@@ -1,0 +1,183 @@
+"""Host-side operators over torch CUDA tensors, calling the C ABI.
+
+torch is used for device memory and streams only.  Names and argument meaning
+follow the reference's benchmark drivers: ``num_segments`` segments of
+``segment_size`` consecutive halves (src/reduction/seg_wmma_16n.cu:14-25); an
+unsupported segment size is an error, as in the reference's dispatch
+(src/reduction/seg_wmma_16n.cu:172 "invalid segment size").
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+OK = 0
+ALGO = {"auto": 0, "mma": 1, "shuffle": 2}
+OUT_F16, OUT_F32 = 0, 1
+OP_SEGMENTED_REDUCE, OP_SEGMENTED_SCAN, OP_FULL_REDUCE, OP_FULL_SCAN = 0, 1, 2, 3
+DIST = {"uniform_pm1": 0, "uniform_01": 1, "small_int": 2, "const_0p001": 3}
+
+
+class TcuError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        msg = _lib.load().tcu_status_string(status).decode()
+        super().__init__(f"{where}: status {status} ({msg})")
+        self.status = status
+
+
+def _check(status: int, where: str) -> None:
+    if status != OK:
+        raise TcuError(status, where)
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _out_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return OUT_F16
+    if dtype == torch.float32:
+        return OUT_F32
+    raise TypeError(f"output dtype must be float16 or float32, got {dtype}")
+
+
+def _require_input(x: torch.Tensor) -> None:
+    if not x.is_cuda:
+        raise RuntimeError("input must be a CUDA tensor: there is no CPU path in this library")
+    if x.dtype != torch.float16 or not x.is_contiguous():
+        raise TypeError("input must be a contiguous float16 tensor")
+
+
+def workspace_bytes(op: int, num_elements: int, segment_size: int) -> int:
+    return int(_lib.load().tcu_workspace_bytes(op, num_elements, segment_size))
+
+
+def _workspace(op: int, n: int, segment_size: int, device, workspace):
+    need = workspace_bytes(op, n, segment_size)
+    if need == 0:
+        return None, 0, 0
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=device)
+    return workspace, workspace.data_ptr(), workspace.numel()
+
+
+def fill(out: torch.Tensor, seed: int, first_index: int = 0, dist: str = "uniform_pm1") -> torch.Tensor:
+    """Fill a float16 CUDA tensor with element i = f(seed, first_index + i)."""
+    _require_input(out)
+    _check(_lib.load().tcu_fill_f16(out.data_ptr(), out.numel(), seed, first_index, DIST[dist],
+                                    _stream()), "tcu_fill_f16")
+    return out
+
+
+def segmented_reduce(x: torch.Tensor, segment_size: int, out_dtype=torch.float32, algo="auto",
+                     out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+    """out[j] = sum(x[j*segment_size:(j+1)*segment_size])."""
+    _require_input(x)
+    n = x.numel()
+    if segment_size <= 0 or n % segment_size:
+        raise ValueError("num_elements must be a multiple of segment_size")
+    segs = n // segment_size
+    if out is None:
+        out = torch.empty(segs, dtype=out_dtype, device=x.device)
+    ws, ws_ptr, ws_bytes = _workspace(OP_SEGMENTED_REDUCE, n, segment_size, x.device, workspace)
+    _check(_lib.load().tcu_segmented_reduce_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype),
+                                                segs, segment_size, ALGO[algo], ws_ptr, ws_bytes,
+                                                _stream()), "tcu_segmented_reduce_f16")
+    return out
+
+
+def segmented_scan(x: torch.Tensor, segment_size: int, out_dtype=torch.float16, algo="auto",
+                   out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+    """Inclusive prefix sum inside every segment of segment_size elements."""
+    _require_input(x)
+    n = x.numel()
+    if segment_size <= 0 or n % segment_size:
+        raise ValueError("num_elements must be a multiple of segment_size")
+    if out is None:
+        out = torch.empty(n, dtype=out_dtype, device=x.device)
+    ws, ws_ptr, ws_bytes = _workspace(OP_SEGMENTED_SCAN, n, segment_size, x.device, workspace)
+    _check(_lib.load().tcu_segmented_scan_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype),
+                                              n // segment_size, segment_size, ALGO[algo], ws_ptr,
+                                              ws_bytes, _stream()), "tcu_segmented_scan_f16")
+    return out
+
+
+def full_reduce(x: torch.Tensor, algo="auto", workspace: torch.Tensor | None = None,
+                out: torch.Tensor | None = None, out_f64: torch.Tensor | None = None):
+    """Sum of all elements; returns (float32[1], float64[1]) device tensors."""
+    _require_input(x)
+    n = x.numel()
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    if out_f64 is None:
+        out_f64 = torch.empty(1, dtype=torch.float64, device=x.device)
+    ws, ws_ptr, ws_bytes = _workspace(OP_FULL_REDUCE, n, n, x.device, workspace)
+    _check(_lib.load().tcu_full_reduce_f16(x.data_ptr(), out.data_ptr(), out_f64.data_ptr(), n,
+                                           ALGO[algo], ws_ptr, ws_bytes, _stream()),
+           "tcu_full_reduce_f16")
+    return out, out_f64
+
+
+def full_scan(x: torch.Tensor, out_dtype=torch.float32, algo="auto",
+              shard_totals: torch.Tensor | None = None, shard_index: int = 0,
+              out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+    """Inclusive prefix sum over the whole tensor (seeded by earlier shards' totals)."""
+    _require_input(x)
+    n = x.numel()
+    if out is None:
+        out = torch.empty(n, dtype=out_dtype, device=x.device)
+    if shard_totals is not None and shard_totals.dtype != torch.float64:
+        raise TypeError("shard_totals must be float64")
+    ws, ws_ptr, ws_bytes = _workspace(OP_FULL_SCAN, n, n, x.device, workspace)
+    st_ptr = shard_totals.data_ptr() if shard_totals is not None else None
+    _check(_lib.load().tcu_full_scan_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype), n,
+                                         st_ptr, shard_index, ALGO[algo], ws_ptr, ws_bytes,
+                                         _stream()), "tcu_full_scan_f16")
+    return out
+
+
+def device_error(clear: bool = True) -> int:
+    """Synchronise and return the device-side error bits (0 = none)."""
+    bits = ctypes.c_uint(0)
+    _lib.load().tcu_device_error(ctypes.byref(bits), 1 if clear else 0)
+    return int(bits.value)
+
+
+class HostContext:
+    """Runs the operators on HOST buffers (pinned torch tensors or numpy arrays).
+
+    Owns two staging buffers of ``chunk_elements`` halves on the device and two
+    streams; host -> device copies, kernels and device -> host copies of
+    consecutive chunks overlap.
+    """
+
+    def __init__(self, chunk_elements: int = 1 << 26):
+        self._ctx = ctypes.c_void_p()
+        _check(_lib.load().tcu_host_ctx_create(ctypes.byref(self._ctx), chunk_elements),
+               "tcu_host_ctx_create")
+
+    def close(self) -> None:
+        if self._ctx:
+            _lib.load().tcu_host_ctx_destroy(self._ctx)
+            self._ctx = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def run(self, op: int, h_in: torch.Tensor, h_out: torch.Tensor, segment_size: int = 0,
+            algo="auto") -> torch.Tensor:
+        if h_in.is_cuda or h_out.is_cuda:
+            raise RuntimeError("HostContext.run takes host tensors")
+        if h_in.dtype != torch.float16 or not h_in.is_contiguous() or not h_out.is_contiguous():
+            raise TypeError("h_in must be contiguous float16, h_out contiguous")
+        _check(_lib.load().tcu_host_run_f16(self._ctx, op, h_in.data_ptr(), h_out.data_ptr(),
+                                            _out_code(h_out.dtype), h_in.numel(), segment_size,
+                                            ALGO[algo]), "tcu_host_run_f16")
+        return h_out
