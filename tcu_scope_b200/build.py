@@ -1,7 +1,8 @@
 """Builds libtcu_scope.so (the C-ABI CUDA library) for sm_100a, in-tree, with nvcc.
 
-Run as ``python -m tcu_scope_b200.build``.  nvcc cross-compiles, so this works
-on a machine without a GPU.
+Run as ``python tcu_scope_b200/build.py`` (a plain script: it must work while
+the library is missing or stale, when the package itself refuses to import).
+nvcc cross-compiles, so this works on a machine without a GPU.
 """
 from __future__ import annotations
 

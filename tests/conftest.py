@@ -29,5 +29,9 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session")
 def built_library():
     """The CUDA library, built in-tree if the sources are newer (nvcc needs no GPU)."""
-    from tcu_scope_b200 import build
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "tcu_scope_b200_build", os.path.join(ROOT, "tcu_scope_b200", "build.py"))
+    build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build)  # by path: the package itself loads the library on import
     return build.build_library()
