@@ -35,7 +35,8 @@ typedef enum {
   TCU_ERR_UNSUPPORTED = 2, /* segment size not a power of two >= 16, unknown algo/type  */
   TCU_ERR_CUDA        = 3, /* a CUDA runtime call failed (see cudaGetLastError)         */
   TCU_ERR_TIMEOUT     = 4, /* a bounded device-side wait ran out (tcu_device_error)     */
-  TCU_ERR_WORKSPACE   = 5  /* workspace missing or smaller than tcu_workspace_bytes()   */
+  TCU_ERR_WORKSPACE   = 5, /* workspace missing or smaller than tcu_workspace_bytes()   */
+  TCU_ERR_TOO_LARGE   = 6  /* more elements than TCU_STATIC_SCAN_MAX_ELEMENTS           */
 } tcu_status;
 
 typedef enum {
@@ -110,6 +111,39 @@ int tcu_full_reduce_f16(const void* d_in, float* d_out, double* d_out_f64, size_
 int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_elements,
                       const double* d_shard_totals, int shard_index, int algo,
                       void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * tcu_full_scan_f16 for callers that must not allocate device memory.  It has
+ * no counterpart in the reference, whose drivers cudaMalloc whatever they need.
+ *
+ * Who needs it: code that runs where cudaMalloc / cudaFree are off limits or
+ * too expensive -- a plugin that was handed its input and output buffers and
+ * nothing else by a host framework that owns all device memory, a service
+ * loop with a latency budget (cudaMalloc and cudaFree synchronise the whole
+ * device), or a step that sits between other asynchronous work and must not
+ * stall it.  Such a caller cannot produce the workspace tcu_full_scan_f16 asks
+ * for, so this variant brings its own: a fixed array in the library's device
+ * image, TCU_STATIC_SCAN_SCRATCH_BYTES (about 0.5 MiB) on every GPU the
+ * library is loaded on, held until the process exits.
+ *
+ * Same arguments and results as tcu_full_scan_f16 minus the workspace.  Limits
+ * and rules that come with the shared array:
+ *   - num_elements <= TCU_STATIC_SCAN_MAX_ELEMENTS (2^30), else TCU_ERR_TOO_LARGE
+ *     and nothing is launched;
+ *   - the first call on each device looks up the array's device address (with
+ *     that device current); make that first call outside any stream capture;
+ *   - every call uses the same array and clears the part it needs on `stream`
+ *     before its kernel, so calls in one stream are fine back to back, but two
+ *     calls that can run at the same time on one GPU (different streams,
+ *     different host threads) race on it: serialise them, or give the second
+ *     one a workspace and use tcu_full_scan_f16;
+ *   - no cudaMalloc, cudaFree or allocating library routine is called.
+ */
+#define TCU_STATIC_SCAN_MAX_ELEMENTS ((size_t)1 << 30)
+#define TCU_STATIC_SCAN_SCRATCH_BYTES (256 + (TCU_STATIC_SCAN_MAX_ELEMENTS / 16384) * 8)
+int tcu_full_scan_f16_static(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                             const double* d_shard_totals, int shard_index, int algo,
+                             void* stream);
 
 /* Bytes of device workspace the operation needs (0 = none).  The workspace
  * needs no initialisation; one workspace must not be shared by calls that can

@@ -23,6 +23,8 @@ SIGNATURES = {
                                     c_size_t, c_void_p]),
     "tcu_full_scan_f16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int, c_int,
                                   c_void_p, c_size_t, c_void_p]),
+    "tcu_full_scan_f16_static": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int,
+                                         c_int, c_void_p]),
     "tcu_workspace_bytes": (c_size_t, [c_int, c_size_t, c_size_t]),
     "tcu_fill_f16": (c_int, [c_void_p, c_size_t, ctypes.c_uint64, ctypes.c_uint64, c_int,
                              c_void_p]),
@@ -46,7 +48,7 @@ def load() -> ctypes.CDLL:
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m tcu_scope_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python tcu_scope_b200/build.py` "
             "(there is no CPU or PyTorch fallback for these operators)")
     lib = ctypes.CDLL(LIB_PATH)
     for name, (restype, argtypes) in SIGNATURES.items():

@@ -27,6 +27,16 @@ constexpr int kDynSmemBytes  = kRingBytes + 128;
 
 int g_sm_count[kMaxDevices];
 
+// Scratch of tcu_full_scan_f16_static: tile-status words of the look-back scan
+// for up to 2^30 elements (65536 tiles x 8 bytes + the 256-byte header).  It
+// lives in every GPU's memory from the moment the library is loaded there.
+// In host code the name below is only a handle for the runtime, never a device
+// address: the address is looked up once per device with cudaGetSymbolAddress.
+constexpr size_t kStaticScanMaxElems = size_t(1) << 30;
+constexpr size_t kStaticScratchBytes = kWsHeader + kStaticScanMaxElems / kTileElems * 8;
+static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScratchBytes];
+void* g_static_scan_scratch_addr[kMaxDevices];  // device address, per device; null = not looked up
+
 int current_device() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
@@ -290,6 +300,28 @@ int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_el
                    static_cast<cudaStream_t>(stream));
 }
 
+int tcu_full_scan_f16_static(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                             const double* d_shard_totals, int shard_index, int algo,
+                             void* stream) {
+  if (num_elements % 16 != 0) return TCU_ERR_INVALID_ARG;
+  if (num_elements > kStaticScanMaxElems) return TCU_ERR_TOO_LARGE;
+  const int dev = current_device();
+  if (dev < 0) return TCU_ERR_CUDA;
+  if (g_static_scan_scratch_addr[dev] == nullptr) {
+    // one-time set-up for this device (it is the current one): resolve the
+    // array's device address; a kernel handed the host-side name would fault
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_static_scan_scratch) != cudaSuccess || addr == nullptr)
+      return TCU_ERR_CUDA;
+    g_static_scan_scratch_addr[dev] = addr;
+  }
+  // scan_impl clears the part of the scratch this call uses (cudaMemsetAsync on
+  // the stream) before the kernel; it allocates nothing.
+  return scan_impl(d_in, d_out, out_type, 1, num_elements, kClassLong, d_shard_totals, shard_index,
+                   algo, g_static_scan_scratch_addr[dev], kStaticScratchBytes,
+                   static_cast<cudaStream_t>(stream));
+}
+
 size_t tcu_workspace_bytes(int op, size_t num_elements, size_t segment_size) {
   switch (op) {
     case TCU_OP_SEGMENTED_REDUCE:
@@ -341,6 +373,7 @@ const char* tcu_status_string(int status) {
     case TCU_ERR_CUDA: return "CUDA runtime error";
     case TCU_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case TCU_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case TCU_ERR_TOO_LARGE: return "input larger than the built-in scratch of the _static entry point";
     default: return "unknown status";
   }
 }
