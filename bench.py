@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--algo", default="auto", choices=["auto", "mma", "shuffle"])
     ap.add_argument("--log2-elems", type=int, default=LOG2_ELEMS,
                     help="elements per GPU (default 28, the reference sweep's size)")
+    ap.add_argument("--profile", default=None, choices=["reduce", "scan", "full"],
+                    help="run ONE untimed pass of the named kernels at --log2-elems and exit "
+                         "(the small case an ncu capture wraps)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other configurations, the e2e leg and the CPU baseline")
     return ap.parse_args()
@@ -316,6 +319,24 @@ def run_e2e(torch, tcu, dist, args, rank, world):
             "note": "pinned host buffers, chunked copies overlapped with kernels on two streams"}
 
 
+def profile_pass(torch, tcu, args, n):
+    """One launch of each kernel of a family, for a profiler to capture."""
+    x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024, 0)
+    if args.profile == "reduce":
+        for s in SWEEP:
+            tcu.segmented_reduce(x, s, algo=args.algo)
+    elif args.profile == "scan":
+        for s, dt in [(16, torch.float16), (256, torch.float16), (4096, torch.float32)]:
+            tcu.segmented_scan(x, s, out_dtype=dt, algo=args.algo)
+    else:
+        tcu.fill(x, 2024, 0, "uniform_01")
+        tcu.full_reduce(x)
+        tcu.full_scan(x, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert tcu.device_error() == 0
+    print(json.dumps({"profile": args.profile, "log2_elems": args.log2_elems, "algo": args.algo}))
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -341,6 +362,9 @@ def main():
     n = 1 << args.log2_elems
     dev = torch.device("cuda")
     peak_gbs, peak_kind = hbm_peak()
+    if args.profile:
+        profile_pass(torch, tcu, args, n)
+        return
 
     # this rank's shard of the logical array: elements [rank*n, (rank+1)*n), two buffers to rotate
     xs = [tcu.fill(torch.empty(n, dtype=torch.float16, device=dev), 2024 + i, rank * n) for i in range(2)]
@@ -413,7 +437,7 @@ def main():
         result["e2e"] = run_e2e(torch, tcu, dist, args, rank, world)
         result["other_configs"] = extras(torch, tcu, dist, args, rank, world, peak_gbs)
         if rank == 0 and world == 1:
-            v, cores, passes, secs = cpu_sweep(26, 8.0, 40)
+            v, cores, passes, secs = cpu_sweep(26, 8.0, 2000)
             result["cpu_baseline"] = {
                 "value": round(v, 3), "unit": "Gelem/s", "cores": cores, "kind": "port",
                 "sample": f"{passes} passes of the 6-size sweep over 2^26 elements ({secs:.1f} s)"}

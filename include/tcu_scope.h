@@ -123,7 +123,7 @@ int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_el
  * device), or a step that sits between other asynchronous work and must not
  * stall it.  Such a caller cannot produce the workspace tcu_full_scan_f16 asks
  * for, so this variant brings its own: a fixed array in the library's device
- * image, TCU_STATIC_SCAN_SCRATCH_BYTES (about 0.5 MiB) on every GPU the
+ * image, TCU_STATIC_SCAN_SCRATCH_BYTES (about 0.8 MiB) on every GPU the
  * library is loaded on, held until the process exits.
  *
  * Same arguments and results as tcu_full_scan_f16 minus the workspace.  Limits
@@ -140,7 +140,9 @@ int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_el
  *   - no cudaMalloc, cudaFree or allocating library routine is called.
  */
 #define TCU_STATIC_SCAN_MAX_ELEMENTS ((size_t)1 << 30)
-#define TCU_STATIC_SCAN_SCRATCH_BYTES (256 + (TCU_STATIC_SCAN_MAX_ELEMENTS / 16384) * 8)
+#define TCU_STATIC_SCAN_MAX_TILES (TCU_STATIC_SCAN_MAX_ELEMENTS / 16384)
+#define TCU_STATIC_SCAN_SCRATCH_BYTES \
+  (256 + TCU_STATIC_SCAN_MAX_TILES * 8 + (TCU_STATIC_SCAN_MAX_TILES / 32 + TCU_STATIC_SCAN_MAX_TILES / 2 + 2) * 8)
 int tcu_full_scan_f16_static(const void* d_in, void* d_out, int out_type, size_t num_elements,
                              const double* d_shard_totals, int shard_index, int algo,
                              void* stream);

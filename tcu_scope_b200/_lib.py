@@ -9,7 +9,9 @@ import ctypes
 import os
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libtcu_scope.so")
+# TCU_SCOPE_LIB selects another build of the same library (e.g. one compiled with
+# different tuning macros); the default is the in-tree build.
+LIB_PATH = os.environ.get("TCU_SCOPE_LIB") or os.path.join(PKG_DIR, "libtcu_scope.so")
 
 c_size_t, c_int, c_void_p = ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p
 

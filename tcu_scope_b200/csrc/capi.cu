@@ -28,12 +28,15 @@ constexpr int kDynSmemBytes  = kRingBytes + 128;
 int g_sm_count[kMaxDevices];
 
 // Scratch of tcu_full_scan_f16_static: tile-status words of the look-back scan
-// for up to 2^30 elements (65536 tiles x 8 bytes + the 256-byte header).  It
+// for up to 2^30 elements (header + a word per tile + the block-level words,
+// about 0.8 MiB).  It
 // lives in every GPU's memory from the moment the library is loaded there.
 // In host code the name below is only a handle for the runtime, never a device
 // address: the address is looked up once per device with cudaGetSymbolAddress.
 constexpr size_t kStaticScanMaxElems = size_t(1) << 30;
-constexpr size_t kStaticScratchBytes = kWsHeader + kStaticScanMaxElems / kTileElems * 8;
+constexpr size_t kStaticScanMaxTiles = kStaticScanMaxElems / kTileElems;
+constexpr size_t kStaticScratchBytes =
+    kWsHeader + kStaticScanMaxTiles * 8 + (kStaticScanMaxTiles / 32 + kStaticScanMaxTiles / 2 + 2) * 8;
 static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScratchBytes];
 void* g_static_scan_scratch_addr[kMaxDevices];  // device address, per device; null = not looked up
 
@@ -107,7 +110,7 @@ cudaError_t launch_scan_lookback(const ScanParams& p, int grid, cudaStream_t st)
   static bool configured[kMaxDevices];
   cudaError_t e = ensure_smem(scan_lookback_kernel<OUT32>, configured, kLookbackDynSmemBytes);
   if (e != cudaSuccess) return e;
-  scan_lookback_kernel<OUT32><<<grid, kThreads, kLookbackDynSmemBytes, st>>>(p);
+  scan_lookback_kernel<OUT32><<<grid, kLookbackThreads, kLookbackDynSmemBytes, st>>>(p);
   return cudaGetLastError();
 }
 
@@ -133,9 +136,13 @@ cudaError_t launch_shuffle_scan(const ScanParams& p, int grid, cudaStream_t st) 
 
 size_t reduce_long_ws_bytes() { return kWsHeader + size_t(2) * kMaxLongGrid * 16; }
 
+// header | one status word per tile | one per block of 32 tiles (+1 per segment
+// for a partial last block; a segment has at least 2 tiles, so tiles/2 bounds it)
+size_t scan_long_tiles(size_t num_elements) { return (num_elements + kTileElems - 1) / kTileElems; }
+
 size_t scan_long_ws_bytes(size_t num_elements) {
-  const size_t tiles = (num_elements + kTileElems - 1) / kTileElems;
-  return kWsHeader + tiles * 8;
+  const size_t tiles = scan_long_tiles(num_elements);
+  return kWsHeader + tiles * 8 + (tiles / 32 + tiles / 2 + 2) * 8;
 }
 
 int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
@@ -226,11 +233,11 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
     uint8_t* w          = static_cast<uint8_t*>(ws);
     p.ticket            = reinterpret_cast<unsigned int*>(w);
     p.tile_status       = reinterpret_cast<unsigned long long*>(w + kWsHeader);
+    p.block_status      = p.tile_status + tiles;
     p.tiles_per_segment = num_segments == 1 ? tiles : segment_size / kTileElems;
     p.shard_totals      = shard_totals;
     p.shard_index       = shard_index;
     if (cudaMemsetAsync(w, 0, need, st) != cudaSuccess) return TCU_ERR_CUDA;
-    // two CTAs per SM: one hides the other's look-back latency
     const size_t want = size_t(sms) * kLookbackCtasPerSm;
     const int lgrid   = tiles < want ? int(tiles) : int(want);
     if (algo == TCU_ALGO_SHUFFLE) return TCU_ERR_UNSUPPORTED;

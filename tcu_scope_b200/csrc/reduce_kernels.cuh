@@ -259,7 +259,9 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
   // Short classes interleave tiles over CTAs; the long class gives each CTA a
   // contiguous run so that a segment's partial sum stays in one register.
   unsigned long long tile_begin, tile_end, tile_step;
-  if constexpr (SC == kClassLong) {
+  // One segment (the full reduction) needs no contiguity either.
+  const bool single = SC == kClassLong && p.num_segments == 1;
+  if (SC == kClassLong && !single) {
     tile_begin = num_tiles * blockIdx.x / gridDim.x;
     tile_end   = num_tiles * (blockIdx.x + 1ull) / gridDim.x;
     tile_step  = 1;
@@ -348,7 +350,8 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
               }
               run_seg     = seg;
               run_val     = 0.0;
-              run_is_head = (tile % p.tiles_per_segment) != 0;  // began in an earlier CTA
+              // began in an earlier CTA (with one segment every CTA holds a piece of it)
+              run_is_head = single || (tile % p.tiles_per_segment) != 0;
             }
             run_val += v;
           }
@@ -395,7 +398,23 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
         sh_val[k] = __ldcg(&p.bound_val[k]);
       }
       __syncthreads();
-      if (threadIdx.x == 0) {
+      if (single) {
+        // every record belongs to segment 0: fixed-shape tree sum over all threads
+        double v = 0.0;
+        for (unsigned int k = threadIdx.x; k < n; k += kThreads)
+          if (sh_seg[k] >= 0) v += sh_val[k];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        __syncthreads();  // everyone has read its records; reuse sh_val for the warp sums
+        if (lane == 0) sh_val[warp] = v;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          double total = 0.0;
+          for (int w = 0; w < kThreads / 32; ++w) total += sh_val[w];
+          store_seg(p.out, p.out_is_f32 != 0, 0, (float)total);
+          if (p.out_f64) p.out_f64[0] = total;
+        }
+      } else if (threadIdx.x == 0) {
         long long cur_seg  = -1;
         double cur         = 0.0;
         const bool out_f32 = p.out_is_f32 != 0;

@@ -32,6 +32,7 @@ struct ScanParams {
   // look-back class only
   unsigned long long tiles_per_segment;  // segment_size / kTileElems
   unsigned long long* tile_status;       // [num_tiles], zeroed by the host before the launch
+  unsigned long long* block_status;      // [~num_tiles/32 + segments], zeroed likewise
   unsigned int* ticket;                  // dynamic tile counter, zeroed by the host
   const double* shard_totals;            // optional: totals of all shards of a multi-GPU scan
   int shard_index;                       // this GPU's position in shard_totals

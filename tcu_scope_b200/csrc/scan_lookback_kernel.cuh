@@ -11,17 +11,45 @@
 // atomic store.  Tiles are handed out by an atomic ticket, which guarantees
 // that every predecessor of a tile already belongs to a running CTA: a wait
 // can only be on work that is making progress.  Every poll loop is bounded.
+//
+// Inside a CTA the look-back is taken off the critical path.  Tile i goes
+//   producer:  TMA load                               -> full[s]
+//   consumers: pass 1 (slice totals, row carries)     -> p1done[s]
+//   one of 4 look-back warps: publish aggregate, walk back, publish prefix
+//                                                     -> resolved[s]
+//   consumers: pass 2 (the scan, seeded), stores      -> empty[s]
+// and the consumers run pass 1 kLookahead tiles ahead of pass 2, so that a
+// tile's aggregate is public long before its successors need it and several
+// look-backs per CTA are in flight while the tensor cores stay busy.
 #pragma once
 
 #include "scan_kernels.cuh"
 
 namespace tcu {
 
-constexpr int kLookbackStages       = 3;
-constexpr int kLookbackCtasPerSm    = 2;  // one CTA computes while the other looks back
-constexpr int kLookbackDynSmemBytes = kLookbackStages * kTileBytes + 128;
+#ifndef TCU_LB_STAGES
+#define TCU_LB_STAGES 6
+#endif
+#ifndef TCU_LB_SAVE_CARRIES
+#define TCU_LB_SAVE_CARRIES 1
+#endif
+constexpr int kLookbackStages       = TCU_LB_STAGES;
+constexpr bool kSaveCarries         = TCU_LB_SAVE_CARRIES != 0;
+#ifndef TCU_LOOKAHEAD
+#define TCU_LOOKAHEAD 4
+#endif
+constexpr int kLookahead            = TCU_LOOKAHEAD;  // pass 1 runs this many tiles ahead of pass 2
+constexpr int kLookbackWarps        = 4;
+constexpr int kLookbackCtasPerSm    = 1;
+constexpr int kLookbackThreads      = (kConsumerWarps + 1 + kLookbackWarps) * 32;
+// one float4 (row carries) per consumer lane, kept from pass 1 to pass 2
+constexpr int kCarryBytesPerStage   = kSaveCarries ? kConsumerWarps * 32 * 16 : 0;
+constexpr int kLookbackDynSmemBytes =
+    kLookbackStages * (kTileBytes + kCarryBytesPerStage) + 128;
+constexpr uint32_t kNoEnd = 0xffffffffu;
 constexpr unsigned long long kTileEnd = ~0ull;
 constexpr unsigned kStateAggregate = 1u, kStateInclusive = 2u;
+constexpr unsigned long long kBlockTiles = 32;  // tiles per second-level status word
 
 __device__ __forceinline__ void status_store(unsigned long long* p, double v, unsigned state) {
   const unsigned long long w =
@@ -35,68 +63,102 @@ __device__ __forceinline__ unsigned long long status_load(const unsigned long lo
   return w;
 }
 
-// Run by all 32 lanes of one warp.  Returns the sum of the aggregates of the
-// tiles [seg_first, tile) -- the exclusive prefix of `tile` inside its segment.
-__device__ __forceinline__ double look_back(const unsigned long long* status,
-                                            unsigned long long tile,
-                                            unsigned long long seg_first, int lane) {
-  double excl    = 0.0;
-  long long base = static_cast<long long>(tile) - 1;  // lane l inspects tile base - l
+// Run by all 32 lanes of one warp.  Walks the status words from index `last`
+// downwards, adding aggregates, until it meets an inclusive prefix (returns
+// with found_inclusive = true: the sum is a complete prefix) or has passed
+// index `first` (found_inclusive = false: the sum covers [first, last] only).
+// Each poll reads one word per lane (256 bytes per warp); words already summed
+// are never read again, and a poll that makes no progress backs off.
+__device__ __forceinline__ double look_back(const unsigned long long* status, long long last,
+                                            long long first, int lane, bool& found_inclusive) {
+  double sum     = 0.0;
   uint32_t polls = 0;
-  while (true) {
-    const long long idx = base - lane;
-    const bool valid    = idx >= static_cast<long long>(seg_first);
-    unsigned long long w = 0;
-    unsigned state       = kStateAggregate;  // tiles before the segment: never used, see below
-    while (true) {
-      if (valid) {
-        w     = status_load(status + idx);
-        state = static_cast<unsigned>(w & 3ull);
-      }
-      if (__all_sync(0xffffffffu, state != 0u)) break;
-      if (++polls > kPollAttempts) {  // give up: wrong result, flagged, but no hang
-        if (lane == 0) raise_error(kErrLookbackTimeout);
-        return excl;
-      }
-      __nanosleep(40);
-    }
-    // The first tile of a segment always publishes an inclusive prefix, so a
-    // window that reaches below seg_first contains an inclusive lane before
-    // any invalid one; invalid lanes are cut off by the mask below.
-    const unsigned incl_mask = __ballot_sync(0xffffffffu, valid && state == kStateInclusive);
-    double v = valid ? __longlong_as_double(static_cast<long long>(w & ~3ull)) : 0.0;
-    if (incl_mask) {
-      const int first = __ffs(incl_mask) - 1;
-      if (lane > first) v = 0.0;
-    }
+  found_inclusive = false;
+  while (last >= first) {
+    const long long idx = last - lane;
+    const bool valid    = idx >= first;
+    const unsigned long long w = valid ? status_load(status + idx) : 0ull;
+    const unsigned state = static_cast<unsigned>(w & 3ull);
+    const unsigned not_ready = __ballot_sync(0xffffffffu, valid && state == 0u);
+    const unsigned stops     = __ballot_sync(0xffffffffu, !valid || state == kStateInclusive);
+    const int z = not_ready ? __ffs(not_ready) - 1 : 32;  // first word nothing is published in
+    const int t = stops ? __ffs(stops) - 1 : 32;          // first inclusive word / end of range
+    const int take = z < t ? z : t;                       // lanes [0, take) hold aggregates
+    double v = 0.0;
+    if (lane < take || (lane == t && t < z && valid))
+      v = __longlong_as_double(static_cast<long long>(w & ~3ull));
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-    excl += v;
-    if (incl_mask) return excl;
-    base -= 32;
+    sum += v;
+    if (t < z) {  // reached an inclusive prefix, or walked past `first`
+      found_inclusive = __shfl_sync(0xffffffffu, valid ? 1 : 0, t) != 0;
+      return sum;
+    }
+    last -= take;
+    if (take == 0) {  // the nearest word is still empty: wait for its tile, but not forever
+      if (++polls > kPollAttempts) {
+        if (lane == 0) raise_error(kErrLookbackTimeout);
+        return sum;  // wrong result, flagged, but no hang
+      }
+      __nanosleep(polls < 8 ? 64 : 256);
+    }
   }
+  return sum;
+}
+
+// try_wait loop that also gives up when the CTA-wide abort flag is raised or,
+// for the look-back warps, when the tile stream has ended before index `idx`.
+__device__ __forceinline__ bool mbar_wait_or_stop(uint32_t bar, uint32_t parity,
+                                                  volatile uint32_t* abort_flag,
+                                                  volatile uint32_t* end_index, uint32_t idx) {
+  for (uint32_t attempt = 0; attempt < kWaitAttempts; ++attempt) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
+        : "memory");
+    if (done) return true;
+    if (*abort_flag) return false;
+    if (end_index != nullptr && *end_index <= idx) return false;
+  }
+  raise_error(kErrBarrierTimeout);
+  *abort_flag = 1u;
+  return false;
 }
 
 template <bool OUT32>
-__global__ void __launch_bounds__(kThreads, kLookbackCtasPerSm)
+__global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     scan_lookback_kernel(const ScanParams p) {
   constexpr int SC = 15;  // row-stream geometry, rows always chained
+  constexpr int NS = kLookbackStages;
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ __align__(8) uint64_t bars[2 * kLookbackStages];
-  __shared__ unsigned long long stage_tile[kLookbackStages];
-  __shared__ float2 part[2][kConsumerWarps];
-  __shared__ double tile_excl[2];
+  __shared__ __align__(8) uint64_t bars[4 * NS];  // full | p1done | resolved | empty
+  __shared__ unsigned long long stage_tile[NS];
+  __shared__ float2 part[NS][kConsumerWarps];      // slice totals (exact hi, lo)
+  __shared__ double tile_excl[NS];                 // exclusive prefix of the tile in its segment
+  __shared__ uint32_t s_abort, s_end_index;
 
   uint8_t* ring = dyn_smem + ((128u - (smem_u32(dyn_smem) & 127u)) & 127u);
+  float4* carries = reinterpret_cast<float4*>(ring + NS * kTileBytes);  // [NS][8][32]
   const uint32_t ring_u32 = smem_u32(ring);
-  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kLookbackStages]);
+  const uint32_t full0 = smem_u32(&bars[0]), p1done0 = smem_u32(&bars[NS]),
+                 resolved0 = smem_u32(&bars[2 * NS]), empty0 = smem_u32(&bars[3 * NS]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile uint32_t* abort_flag = &s_abort;
+  volatile uint32_t* end_index  = &s_end_index;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kLookbackStages; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(full0 + 8 * s, 1);
+      mbar_init(p1done0 + 8 * s, kConsumerWarps);
+      mbar_init(resolved0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, kConsumerWarps);
     }
+    s_abort     = 0u;
+    s_end_index = kNoEnd;
     mbar_fence_init();
   }
   __syncthreads();
@@ -105,10 +167,11 @@ __global__ void __launch_bounds__(kThreads, kLookbackCtasPerSm)
   const unsigned long long num_tiles   = (total_bytes + kTileBytes - 1) / kTileBytes;
 
   if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------ producer
     if (lane == 0) {
       for (uint32_t i = 0;; ++i) {
-        const uint32_t s = i % kLookbackStages, ph = (i / kLookbackStages) & 1u;
-        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) break;
+        const uint32_t s = i % NS, ph = (i / NS) & 1u;
+        if (!mbar_wait_or_stop(empty0 + 8 * s, ph ^ 1u, abort_flag, nullptr, 0)) break;
         const unsigned long long tile = atomicAdd(p.ticket, 1u);
         if (tile >= num_tiles) {
           stage_tile[s] = kTileEnd;
@@ -126,82 +189,165 @@ __global__ void __launch_bounds__(kThreads, kLookbackCtasPerSm)
     return;
   }
 
+  if (warp > kConsumerWarps) {
+    // ------------------------------------------------------ look-back warps
+    for (uint32_t i = warp - kConsumerWarps - 1;; i += kLookbackWarps) {
+      const uint32_t s = i % NS, ph = (i / NS) & 1u;
+      if (!mbar_wait_or_stop(p1done0 + 8 * s, ph, abort_flag, end_index, i)) break;
+      const unsigned long long tile = stage_tile[s];
+      double agg = 0.0;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) agg += (double)part[s][w].x + (double)part[s][w].y;
+      // Two levels: tiles inside a block of kBlockTiles tiles, then whole blocks
+      // (block b of a segment = tiles [seg_first + b*32, +32)).  A walk is at
+      // most one window inside the block plus about one window over blocks,
+      // however many tiles are in flight on the machine.
+      const unsigned long long tps       = p.tiles_per_segment;
+      const unsigned long long seg_first = (tile / tps) * tps;
+      const unsigned long long rel       = tile - seg_first;
+      const unsigned long long blk       = rel / kBlockTiles;            // block inside the segment
+      const unsigned long long blk_first = seg_first + blk * kBlockTiles;
+      // block status words of all segments, one run of words per segment
+      const unsigned long long blk_base = (seg_first / tps) * ((tps + kBlockTiles - 1) / kBlockTiles);
+      const bool closes_block = (rel % kBlockTiles) == kBlockTiles - 1 && rel + 1 < tps;
+      double excl = 0.0;
+      if (rel == 0) {
+        if (tile == 0 && p.shard_totals != nullptr)  // earlier shards of a multi-GPU scan
+          for (int k = 0; k < p.shard_index; ++k) excl += p.shard_totals[k];
+        if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
+      } else {
+        if (lane == 0) status_store(p.tile_status + tile, agg, kStateAggregate);
+        bool complete = false;
+        const double in_block = look_back(p.tile_status, (long long)tile - 1,
+                                          (long long)blk_first, lane, complete);
+        double before_block = 0.0;
+        if (!complete) {  // blk > 0 here: block 0 starts with the segment's inclusive first tile
+          if (closes_block && lane == 0)
+            status_store(p.block_status + blk_base + blk, in_block + agg, kStateAggregate);
+          bool dummy;
+          before_block = look_back(p.block_status, (long long)(blk_base + blk) - 1,
+                                   (long long)blk_base, lane, dummy);
+        }
+        excl = before_block + in_block;
+        if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
+      }
+      // the last tile of a block publishes the prefix through the block
+      if (closes_block && lane == 0)
+        status_store(p.block_status + blk_base + blk, excl + agg, kStateInclusive);
+      if (lane == 0) {
+        tile_excl[s] = excl;
+        mbar_arrive(resolved0 + 8 * s);  // release: tile_excl is visible to the waiters
+      }
+    }
+    return;
+  }
+
+  // --------------------------------------------------------------- consumers
   using Geom = ScanGeom<SC>;
   const int g = lane >> 2, t = lane & 3;
   const ScanOperands ops = make_scan_operands(lane);
   const Acc zero{0.f, 0.f, 0.f, 0.f};
 
-  for (uint32_t i = 0;; ++i) {
-    const uint32_t s = i % kLookbackStages, ph = (i / kLookbackStages) & 1u;
-    // All eight warps wait on the same phase, so they give up together.
-    if (!mbar_wait(full0 + 8 * s, ph)) break;
+  struct SliceView {
+    uint8_t* slice;
+    unsigned long long slice_off;
+    int valid_bytes;
+  };
+  auto slice_view = [&](uint32_t s, unsigned long long tile) {
+    SliceView v;
+    v.slice     = ring + s * kTileBytes + warp * kSliceBytes;
+    v.slice_off = tile * kTileBytes + (unsigned long long)warp * kSliceBytes;
+    const long long left = (long long)total_bytes - (long long)v.slice_off;
+    v.valid_bytes = left <= 0 ? 0 : (left < kSliceBytes ? (int)left : kSliceBytes);
+    return v;
+  };
+
+  // pass 1 of local tile i: slice total and row carries.  false = no such tile.
+  auto pass1 = [&](uint32_t i) -> bool {
+    const uint32_t s = i % NS, ph = (i / NS) & 1u;
+    if (!mbar_wait_or_stop(full0 + 8 * s, ph, abort_flag, nullptr, 0)) return false;
     const unsigned long long tile = stage_tile[s];
-    if (tile == kTileEnd) break;
-
-    uint8_t* slice = ring + s * kTileBytes + warp * kSliceBytes;
-    const unsigned long long slice_off = tile * kTileBytes + (unsigned long long)warp * kSliceBytes;
-    const long long left  = (long long)total_bytes - (long long)slice_off;
-    const int valid_bytes = left <= 0 ? 0 : (left < kSliceBytes ? (int)left : kSliceBytes);
-    const bool active     = valid_bytes > 0;
-    if (active && valid_bytes < kSliceBytes) zero_slice_tail(slice, valid_bytes, lane);
-
-    // ---- pass 1 over the slice: row totals
+    if (tile == kTileEnd) {
+      if (lane == 0) *end_index = i;  // lets the look-back warps leave
+      return false;
+    }
+    const SliceView v = slice_view(s, tile);
+    const bool active = v.valid_bytes > 0;
+    if (active && v.valid_bytes < kSliceBytes) zero_slice_tail(v.slice, v.valid_bytes, lane);
     Acc tot_h = zero, tot_l = zero;
     if (active) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
-        load_split<Geom>(slice, g, t, j, ah, al);
+        load_split<Geom>(v.slice, g, t, j, ah, al);
         tot_h = mma_ones(ah, tot_h);
         tot_l = mma_ones(al, tot_l);
       }
     }
     float ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l;
     row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
-    if (lane == 0) part[i & 1][warp] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
-    consumer_sync();
+    if constexpr (kSaveCarries)
+      carries[(s * kConsumerWarps + warp) * 32 + lane] = make_float4(ch_lo, cl_lo, ch_hi, cl_hi);
+    if (lane == 0) part[s][warp] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(p1done0 + 8 * s);
+    return true;
+  };
 
-    // ---- warp 0: publish this tile, find its exclusive prefix
-    if (warp == 0) {
-      double agg = 0.0;
-#pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w)
-        agg += (double)part[i & 1][w].x + (double)part[i & 1][w].y;
-      const unsigned long long seg_first = (tile / p.tiles_per_segment) * p.tiles_per_segment;
-      double excl = 0.0;
-      if (tile == seg_first) {
-        if (tile == 0 && p.shard_totals != nullptr)  // earlier shards of a multi-GPU scan
-          for (int k = 0; k < p.shard_index; ++k) excl += p.shard_totals[k];
-        if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
-      } else {
-        if (lane == 0) status_store(p.tile_status + tile, agg, kStateAggregate);
-        excl = look_back(p.tile_status, tile, seg_first, lane);
-        if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
-      }
-      if (lane == 0) tile_excl[i & 1] = excl;
-    }
-    consumer_sync();
-
-    // ---- carry into this slice: tile prefix + earlier slices of the tile, as two floats
-    double carry = tile_excl[i & 1];
-    for (int w = 0; w < warp; ++w) carry += (double)part[i & 1][w].x + (double)part[i & 1][w].y;
+  // pass 2 of local tile k: the scan proper, seeded with everything before the slice
+  auto pass2 = [&](uint32_t k) -> bool {
+    const uint32_t s = k % NS, ph = (k / NS) & 1u;
+    if (!mbar_wait_or_stop(resolved0 + 8 * s, ph, abort_flag, nullptr, 0)) return false;
+    const unsigned long long tile = stage_tile[s];
+    const SliceView v = slice_view(s, tile);
+    double carry = tile_excl[s];
+    for (int w = 0; w < warp; ++w) carry += (double)part[s][w].x + (double)part[s][w].y;
     const float xh = (float)carry;
     const float xl = (float)(carry - (double)xh);
-
-    // ---- pass 2: the scans proper
-    if (active) {
-      const unsigned long long elem_base = slice_off / 2;
-      const int valid_elems = valid_bytes / 2;
+    if (v.valid_bytes > 0) {
+      float ch_lo, cl_lo, ch_hi, cl_hi;
+      if constexpr (kSaveCarries) {
+        const float4 c = carries[(s * kConsumerWarps + warp) * 32 + lane];
+        ch_lo = c.x, cl_lo = c.y, ch_hi = c.z, cl_hi = c.w;
+      } else {  // no room to keep them: redo the row totals
+        Acc tot_h = zero, tot_l = zero;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t ah[4], al[4];
+          load_split<Geom>(v.slice, g, t, j, ah, al);
+          tot_h = mma_ones(ah, tot_h);
+          tot_l = mma_ones(al, tot_l);
+        }
+        float slice_h, slice_l;
+        row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
+      }
+      const unsigned long long elem_base = v.slice_off / 2;
+      const int valid_elems = v.valid_bytes / 2;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
-        load_split<Geom>(slice, g, t, j, ah, al);
+        load_split<Geom>(v.slice, g, t, j, ah, al);
         scan_step<SC, OUT32, true>(j, ah, al, ops, ch_lo, cl_lo, ch_hi, cl_hi, xh, xl, p.out,
                                    elem_base, valid_elems, g, t);
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    return true;
+  };
+
+  uint32_t p1_next = 0;
+  bool more = true;
+  while (more && p1_next < (uint32_t)kLookahead) {
+    more = pass1(p1_next);
+    if (more) ++p1_next;
+  }
+  for (uint32_t k = 0; k < p1_next; ++k) {
+    if (!pass2(k)) break;
+    if (more) {
+      more = pass1(p1_next);
+      if (more) ++p1_next;
+    }
   }
 }
 
