@@ -198,3 +198,26 @@ def c_check_f16(got_bits: np.ndarray, ref: np.ndarray, max_ulp: int = 2):
     worst = ctypes.c_int(0)
     bad = c_lib().tcu_oracle_check_f16(_ptr(g), _ptr(r), g.size, max_ulp, ctypes.byref(worst))
     return int(bad), worst.value
+
+
+# ------------------------------------------------- the reference's own kernels
+REF_LIB_PATH = os.path.join(HERE, "_ref", "libtcu_ref.so")
+_ref = None
+
+
+def ref_lib():
+    """oracle/_ref/libtcu_ref.so: the reference's WMMA kernels compiled unmodified for
+    sm_100a by ``make -C oracle ref`` (needs the reference checkout; the built file
+    travels to the GPU box).  Returns None when it has not been built."""
+    global _ref
+    if _ref is not None:
+        return _ref
+    if not os.path.exists(REF_LIB_PATH):
+        return None
+    lib = ctypes.CDLL(REF_LIB_PATH)
+    vp, sz, i32 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    for name in ("tcu_ref_segmented_reduce", "tcu_ref_segmented_scan"):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = i32, [vp, vp, sz, sz, i32, i32, vp]
+    _ref = lib
+    return lib

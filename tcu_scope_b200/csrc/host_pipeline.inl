@@ -78,7 +78,6 @@ int tcu_host_run_f16(tcu_host_ctx* c, int op, const void* h_in, void* h_out, int
   if (!c || !h_in || !h_out) return TCU_ERR_INVALID_ARG;
   if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
   const bool segmented = op == TCU_OP_SEGMENTED_REDUCE || op == TCU_OP_SEGMENTED_SCAN;
-  const bool reduce    = op == TCU_OP_SEGMENTED_REDUCE || op == TCU_OP_FULL_REDUCE;
   if (!segmented && op != TCU_OP_FULL_REDUCE && op != TCU_OP_FULL_SCAN) return TCU_ERR_UNSUPPORTED;
   if (num_elements == 0) return segmented ? TCU_OK : TCU_ERR_INVALID_ARG;
   size_t chunk = c->chunk_elems;
