@@ -32,9 +32,10 @@ sys.path.insert(0, ROOT)
 LOG2_ELEMS = 28
 SWEEP = [16, 32, 64, 256, 1024, 16384]
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
-# dram__bytes_read.sum + dram__bytes_write.sum of one seg_reduce_kernel<4> launch over 2^28
-# elements, from the ncu capture summarised in profiles/; None until measured.
-NCU_TRAFFIC_BYTES_S16 = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one seg_reduce_kernel<4> launch: captured by
+# ncu at 2^27 elements (268.457 MB read + 24.755 MB written, profiles/seg_reduce_kernel_sweep_2p27.md)
+# and doubled for the 2^28-element launch of this benchmark (traffic grows with the element count).
+NCU_TRAFFIC_BYTES_S16 = 2 * (268_457_472 + 24_755_200)
 
 
 def parse_args():
@@ -65,48 +66,62 @@ def hbm_peak():
 
 
 class ClockSampler:
-    """nvidia-smi sampled every 200 ms while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, read through NVML every few milliseconds
+    while the timed region runs (read-only queries; nothing is set)."""
 
-    def __init__(self, index: int):
-        self.proc = None
+    def __init__(self, index: int, period_s: float = 0.002):
+        import threading
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except Exception:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # no NVML: report that instead of a number
+            self._nvml = None
+            self.reasons.add(f"nvml unavailable: {type(e).__name__}")
+            return
+        self._period = period_s
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        n = self._nvml
+        bits = {
+            "hw_slowdown": getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+                r = get_reasons(self._h)
+                for name, bit in bits.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self._period)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except Exception:
-            self.proc.kill()
-            out = ""
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
-                "reasons": sorted(reasons)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "samples": len(self.samples),
+                "reasons": sorted(self.reasons)}
 
 
 # --------------------------------------------------------------------------- CPU arm
@@ -177,24 +192,56 @@ def workload_config(args, world: int):
             "elements_per_gpu": 1 << args.log2_elems, "segment_sizes": SWEEP,
             "sharding": f"whole segments over {world} GPU(s), no communication",
             "l2": "inputs (512 MiB) exceed L2 (126 MB) and rotate over 2 buffers",
+            "timing": "one CUDA-graph replay (6 launches) per step, CUDA events around the K steps",
             "algo": args.algo}
 
 
 # --------------------------------------------------------------------------- GPU arm
 def time_op(torch, fn, reps: int, warm: int = 3):
-    """Median and min CUDA-event time (ms) of fn() on the current stream."""
+    """Average CUDA-event time (ms) of fn() over `reps` back-to-back calls on the current
+    stream, taken twice: returns (mean of the two batches, the faster batch)."""
     for _ in range(warm):
         fn()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(reps)]
-    torch.cuda.synchronize()
-    for a, b in evs:
+    out = []
+    for _ in range(2):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
         a.record()
-        fn()
+        for _ in range(reps):
+            fn()
         b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) / reps)
+    return statistics.mean(out), min(out)
+
+
+def time_graph(torch, fn, launches_per_graph: int, replays: int):
+    """fn() is called launches_per_graph times inside one CUDA graph; the graph is replayed
+    `replays` times between two events.  Returns ms per fn() call.  For launches far shorter
+    than the host's launch overhead (the 2^24-element configuration: ~10 us of GPU work)."""
+    for _ in range(launches_per_graph):
+        fn()
     torch.cuda.synchronize()
-    ts = [a.elapsed_time(b) for a, b in evs]
-    return statistics.median(ts), min(ts)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(launches_per_graph):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    g.replay()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(2):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) / (replays * launches_per_graph))
+    return statistics.mean(out), min(out)
 
 
 def extras(torch, tcu, dist, args, rank, world, peak_gbs):
@@ -222,7 +269,8 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
         i = k[0] % 8
         k[0] += 1
         tcu.segmented_reduce(xs[i], 16, out=os_[i], algo=args.algo)
-    out["C1_seg_reduce_2^24_S16_cold"] = entry(n24, 2.25, *time_op(torch, c1, 40, 8))
+    out["C1_seg_reduce_2^24_S16_cold"] = entry(n24, 2.25, *time_graph(torch, c1, 16, 10))
+    out["C1_seg_reduce_2^24_S16_cold"]["timing"] = "16 launches per CUDA graph, 8 rotating buffer sets"
     del xs, os_
 
     x = [tcu.fill(torch.empty(n28, dtype=torch.float16, device=dev), 2, rank * n28 + i * (1 << 40))
@@ -276,6 +324,47 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_med, ms_min = t.tolist()
     out["C5_full_scan_2^30_per_gpu_f32"] = entry(n30 * world, 6, ms_med, ms_min)
+    return out
+
+
+def reference_kernels_leg(torch, tcu, args):
+    """Baseline leg, beside the CPU one: the reference's OWN WMMA kernels (compiled unmodified
+    for sm_100a into oracle/_ref where the reference checkout was present) timed on this GPU on
+    the same sweep.  They accumulate and store fp16 and are not checked here; the tests compare
+    them with the oracle on exactly summable inputs.  Returns None when the file is missing."""
+    import oracle
+    ref = oracle.ref_lib()
+    if ref is None:
+        return None
+    n = 1 << min(args.log2_elems, 28)
+    x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024, 0)
+    stream = torch.cuda.current_stream().cuda_stream
+    # the launch shapes the reference's own plots pick (figures/spec/segmented_reduction_16n.yml:30-42,
+    # paper_tune_segmented_reduction.yml:36-48, paper_tune_segmented_prefixsum.yml:30-54)
+    reduce_shapes = {16: (0, 8), 32: (0, 8), 64: (0, 8), 256: (1, 8), 1024: (1, 8), 16384: (1, 8)}
+    scan_shapes = {16: (0, 8), 256: (1, 8), 4096: (1, 4)}
+    out = {"reduce_gelem_per_s": {}, "scan_f16_gelem_per_s": {}}
+    total_ms = 0.0
+    for s, (variant, wpb) in reduce_shapes.items():
+        o = torch.empty(n // s, dtype=torch.float16, device="cuda")
+
+        def call():
+            rc = ref.tcu_ref_segmented_reduce(x.data_ptr(), o.data_ptr(), n // s, s, variant, wpb, stream)
+            assert rc == 0, rc
+        ms, _ = time_op(torch, call, 5, 2)
+        total_ms += ms
+        out["reduce_gelem_per_s"][str(s)] = round(n / ms / 1e6, 1)
+    out["sweep_gelem_per_s"] = round(len(reduce_shapes) * n / total_ms / 1e6, 1)
+    for s, (variant, wpb) in scan_shapes.items():
+        o = torch.empty(n, dtype=torch.float16, device="cuda")
+
+        def call():
+            rc = ref.tcu_ref_segmented_scan(x.data_ptr(), o.data_ptr(), n // s, s, variant, wpb, stream)
+            assert rc == 0, rc
+        ms, _ = time_op(torch, call, 5, 2)
+        out["scan_f16_gelem_per_s"][str(s)] = round(n / ms / 1e6, 1)
+        del o
+    out["note"] = "reference kernels, fp16 accumulate and fp16 outputs, unvalidated at this size"
     return out
 
 
@@ -371,50 +460,81 @@ def main():
     outs = {s: torch.empty(n // s, dtype=torch.float32, device=dev) for s in SWEEP}
     counter = [0]
 
-    def step(events=None):
-        for j, s in enumerate(SWEEP):
-            x = xs[counter[0] % 2]
-            counter[0] += 1
-            if events is not None:
-                events[j][0].record()
-            tcu.segmented_reduce(x, s, out=outs[s], algo=args.algo)
-            if events is not None:
-                events[j][1].record()
+    def launch(s):
+        x = xs[counter[0] % 2]  # consecutive launches alternate between the two input buffers
+        counter[0] += 1
+        tcu.segmented_reduce(x, s, out=outs[s], algo=args.algo)
+
+    def step():
+        for s in SWEEP:
+            launch(s)
+
+    def capture(fn):
+        """fn() captured into one CUDA graph (every launch goes through the C ABI on the
+        capturing stream); None if capture is not possible."""
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    fn()
+            torch.cuda.current_stream().wait_stream(side)
+            g.replay()
+            torch.cuda.synchronize()
+            return g
+        except Exception as e:  # keep measuring, say why
+            print(f"warning: CUDA graph capture failed ({e}); timing direct launches", file=sys.stderr)
+            return None
+
+    step()  # first call of every kernel: one-time function attributes, before any capture
+    torch.cuda.synchronize()
+    step_graph = capture(step)  # six launches; an even count, so replays keep alternating buffers
+    run_step = step_graph.replay if step_graph is not None else step
 
     for _ in range(max(args.warmup, 0)):
-        step()
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in SWEEP] for _ in range(args.steps)]
+        run_step()
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     t_begin.record()
     for k in range(args.steps):
-        step(ev[k])
+        run_step()
     t_end.record()
     torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
     if world > 1:
         dist.barrier()
-    clocks = sampler.stop() if sampler else None
     total_ms = t_begin.elapsed_time(t_end)
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms = float(t[0])
     assert tcu.device_error() == 0, "a bounded device-side wait ran out"
+    value = args.steps * len(SWEEP) * n * world / (total_ms * 1e-3) / 1e9
 
+    # Per-kernel durations: every size on its own, six back-to-back launches per graph replay,
+    # CUDA events around `steps` replays on the launching stream.
     per_size = {}
-    for j, s in enumerate(SWEEP):
-        ts = [ev[k][j][0].elapsed_time(ev[k][j][1]) for k in range(args.steps)]
-        ms = statistics.mean(ts)
+    for s in SWEEP:
+        g = capture(lambda: [launch(s) for _ in range(6)])
+        fn = g.replay if g is not None else (lambda: [launch(s) for _ in range(6)])
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(max(args.steps, 1)):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / (6 * max(args.steps, 1))
         bpe = 2 + 4 / s
         per_size[str(s)] = {"ms": round(ms, 4), "gelem_per_s": round(n / ms / 1e6, 1),
                             "gbytes_per_s": round(n * bpe / ms / 1e6, 1),
                             "hbm_frac": round(n * bpe / ms / 1e6 / peak_gbs, 4)}
-    value = args.steps * len(SWEEP) * n * world / (total_ms * 1e-3) / 1e9
 
     # dominant kernel: the 16-element launch moves the most bytes (2 + 4/16 per element)
     dom = per_size["16"]
@@ -422,6 +542,7 @@ def main():
                 "achieved": dom["gbytes_per_s"], "peak": peak_gbs, "unit": "GB/s",
                 "frac": dom["hbm_frac"], "peak_source": f"of {peak_kind}",
                 "algorithmic_bytes_per_launch": int(n * 2.25),
+                "timing": "back-to-back launches of this kernel (6 per graph replay), CUDA events",
                 "traffic": NCU_TRAFFIC_BYTES_S16 if args.log2_elems == 28 else None}
 
     result = {
@@ -441,6 +562,9 @@ def main():
             result["cpu_baseline"] = {
                 "value": round(v, 3), "unit": "Gelem/s", "cores": cores, "kind": "port",
                 "sample": f"{passes} passes of the 6-size sweep over 2^26 elements ({secs:.1f} s)"}
+            rk = reference_kernels_leg(torch, tcu, args)
+            if rk is not None:
+                result["reference_kernels_on_this_gpu"] = rk
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

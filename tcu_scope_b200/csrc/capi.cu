@@ -7,6 +7,7 @@
 
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <new>
 
 #include "common.cuh"
@@ -105,12 +106,52 @@ cudaError_t launch_scan(const ScanParams& p, int grid, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-template <bool OUT32>
-cudaError_t launch_scan_lookback(const ScanParams& p, int grid, cudaStream_t st) {
+// cuTensorMapEncodeTiled, looked up once through the runtime (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool looked_up   = false;
+  if (!looked_up) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    looked_up = true;
+  }
+  return fn;
+}
+
+// 2-D view of the fp16 input for the swizzled tile loads: rows of 64 halves
+// (128 bytes), one box = one tile = 256 rows.  False if the view cannot be made
+// (element count not a multiple of 64, or no encoder): callers fall back to
+// linear copies.
+bool make_input_tensor_map(CUtensorMap* map, const void* d_in, size_t num_elems) {
+  if (num_elems % kSwizzleRowElems != 0) return false;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2]    = {kSwizzleRowElems, num_elems / kSwizzleRowElems};
+  const cuuint64_t strides[1] = {kSwizzleRowElems * 2};
+  const cuuint32_t box[2]     = {kSwizzleRowElems, kTileRows};
+  const cuuint32_t estr[2]    = {1, 1};
+  if (dims[1] >= (cuuint64_t(1) << 32)) return false;
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(d_in), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool OUT32, bool kSwz>
+cudaError_t launch_scan_lookback(const ScanParams& p, const CUtensorMap& map, int grid,
+                                 cudaStream_t st) {
   static bool configured[kMaxDevices];
-  cudaError_t e = ensure_smem(scan_lookback_kernel<OUT32>, configured, kLookbackDynSmemBytes);
+  cudaError_t e =
+      ensure_smem(scan_lookback_kernel<OUT32, kSwz>, configured, kLookbackDynSmemBytes);
   if (e != cudaSuccess) return e;
-  scan_lookback_kernel<OUT32><<<grid, kLookbackThreads, kLookbackDynSmemBytes, st>>>(p);
+  scan_lookback_kernel<OUT32, kSwz><<<grid, kLookbackThreads, kLookbackDynSmemBytes, st>>>(p, map);
   return cudaGetLastError();
 }
 
@@ -241,7 +282,14 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
     const size_t want = size_t(sms) * kLookbackCtasPerSm;
     const int lgrid   = tiles < want ? int(tiles) : int(want);
     if (algo == TCU_ALGO_SHUFFLE) return TCU_ERR_UNSUPPORTED;
-    e = f32 ? launch_scan_lookback<true>(p, lgrid, st) : launch_scan_lookback<false>(p, lgrid, st);
+    CUtensorMap map;
+    std::memset(&map, 0, sizeof(map));
+    if (make_input_tensor_map(&map, d_in, n))
+      e = f32 ? launch_scan_lookback<true, true>(p, map, lgrid, st)
+              : launch_scan_lookback<false, true>(p, map, lgrid, st);
+    else
+      e = f32 ? launch_scan_lookback<true, false>(p, map, lgrid, st)
+              : launch_scan_lookback<false, false>(p, map, lgrid, st);
   } else if (algo == TCU_ALGO_SHUFFLE) {
     switch (sc) {
 #define X(C)                                                                         \
@@ -367,6 +415,19 @@ int tcu_device_error(unsigned int* bits, int clear) {
   if (bits) *bits = v;
   return v ? TCU_ERR_TIMEOUT : TCU_OK;
 }
+
+#ifdef TCU_LB_PROFILE
+// debug build only: look-back timing counters (see scan_lookback_kernel.cuh)
+int tcu_debug_lookback_stats(unsigned long long* out8, int clear) {
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(out8, g_lb_stats, 64) != cudaSuccess) return TCU_ERR_CUDA;
+  if (clear) {
+    unsigned long long z[8] = {0};
+    cudaMemcpyToSymbol(g_lb_stats, z, 64);
+  }
+  return TCU_OK;
+}
+#endif
 
 int tcu_tile_elements(void) { return kTileElems; }
 

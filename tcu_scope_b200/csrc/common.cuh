@@ -3,6 +3,7 @@
 // m16n8k16 tensor-core contraction and the constant operands it is fed.
 #pragma once
 
+#include <cuda.h>  // CUtensorMap (the type only; the encoder is looked up at run time)
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -88,6 +89,27 @@ __device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src_g
       ::"r"(dst_smem), "l"(src_gmem), "r"(bytes), "r"(bar)
       : "memory");
 }
+
+// Tiled TMA through a tensor map: one box of the 2-D view {64 halves, rows} of
+// the input lands in shared memory with the 128-byte swizzle applied (16-byte
+// chunk index XOR row index mod 8), which is what makes the scan kernels'
+// row-strided 8-byte loads conflict-free.  c0 is an element coordinate (a
+// multiple of 8 elements = 16 bytes), c1 a row coordinate; rows past the end
+// of the tensor arrive as zeros and still count towards the byte total.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* tmap, int c0,
+                                            int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+constexpr int kSwizzleRowElems = 64;                  // 128-byte rows of the tensor view
+constexpr int kTileRows = kTileElems / kSwizzleRowElems;  // 256 rows per tile (the box height)
+
+// Byte offset inside a 1024-byte-aligned tile after the 128-byte swizzle.
+__device__ __forceinline__ int swizzle128(int off) { return off ^ (((off >> 7) & 7) << 4); }
 
 // Named barrier over the consumer warps only (the producer warp never joins).
 __device__ __forceinline__ void consumer_sync() {

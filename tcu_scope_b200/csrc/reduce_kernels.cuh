@@ -237,6 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kStages];
   __shared__ float2 part[2][kConsumerWarps];  // slice totals of the tile in flight
+  __shared__ double warp_sum[kConsumerWarps]; // full reduction: per-warp running sums
   __shared__ int s_is_last;
 
   // 128-byte aligned ring, whatever offset the dynamic segment starts at
@@ -293,6 +294,13 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
     double run_val    = 0.0;
     long long run_seg = -1;
     bool run_is_head  = false;
+    // segment of the next tile and the tile's position inside it (long class, warp 0 lane 0)
+    long long next_seg = 0;
+    unsigned long long tile_in_seg = 0;
+    if (SC == kClassLong && !single) {
+      next_seg    = (long long)(tile_begin / p.tiles_per_segment);
+      tile_in_seg = tile_begin % p.tiles_per_segment;
+    }
     if (SC == kClassLong && warp == 0 && lane == 0) {
       p.bound_seg[2 * blockIdx.x] = -1;
       p.bound_seg[2 * blockIdx.x + 1] = -1;
@@ -321,6 +329,11 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
 
+      if (single) {
+        // one segment: no per-tile meeting of the warps, each keeps its own running sum
+        run_val += (double)tot.x + (double)tot.y;
+        continue;
+      }
       if constexpr (SC >= 12) {
         // combine the slice totals of this tile across warps
         if (lane == 0) part[i & 1][warp] = tot;
@@ -337,7 +350,13 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
               store_seg(p.out, out_f32, seg, (float)v);
           } else if (lane == 0) {
             // v = exact total of this tile; extend or flush the running segment
-            const long long seg = (long long)(tile / p.tiles_per_segment);
+            // segment of this tile without a 64-bit division per tile: tiles of a
+            // CTA are consecutive here (or all in segment 0)
+            if (!single && run_seg >= 0 && ++tile_in_seg == p.tiles_per_segment) {
+              tile_in_seg = 0;
+              ++next_seg;
+            }
+            const long long seg = next_seg;
             if (seg != run_seg) {
               if (run_seg >= 0) {
                 if (run_is_head) {
@@ -351,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
               run_seg     = seg;
               run_val     = 0.0;
               // began in an earlier CTA (with one segment every CTA holds a piece of it)
-              run_is_head = single || (tile % p.tiles_per_segment) != 0;
+              run_is_head = single || tile_in_seg != 0;
             }
             run_val += v;
           }
@@ -360,7 +379,17 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
     }
 
     if constexpr (SC == kClassLong) {
-      if (warp == 0 && lane == 0 && run_seg >= 0) {
+      if (single) {  // the warps' running sums meet once, in warp order
+        if (lane == 0) warp_sum[warp] = run_val;
+        consumer_sync();
+        if (warp == 0 && lane == 0) {
+          double total = 0.0;
+          for (int w = 0; w < kConsumerWarps; ++w) total += warp_sum[w];
+          p.bound_val[2 * blockIdx.x] = total;
+          p.bound_seg[2 * blockIdx.x] = 0;
+          __threadfence();
+        }
+      } else if (warp == 0 && lane == 0 && run_seg >= 0) {
         const bool ends_here = (tile_end % p.tiles_per_segment) == 0;  // segment complete
         if (run_is_head) {
           p.bound_val[2 * blockIdx.x] = run_val;

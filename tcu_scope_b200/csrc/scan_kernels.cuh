@@ -87,11 +87,15 @@ struct ScanGeom {
 // Load the 2 x 8 bytes lane (g,t) owns at step j and split them into exact
 // hi / lo A operands: [0] row g k 2t,2t+1  [1] row g+8 k 2t,2t+1
 //                     [2] row g k 2t+8,+9  [3] row g+8 k 2t+8,+9.
-template <class Geom>
+// kSwz: the tile was written by a swizzled tensor-map copy (slices start on
+// 4 KiB boundaries of a 1 KiB-aligned tile, so the swizzle only depends on the
+// offset inside the slice).
+template <class Geom, bool kSwz = false>
 __device__ __forceinline__ void load_split(const uint8_t* slice, int g, int t, int j,
                                            uint32_t (&ah)[4], uint32_t (&al)[4]) {
-  const uint2 lo = lds64(slice + Geom::lo(g, t, j));
-  const uint2 hi = lds64(slice + Geom::lo(g, t, j) + Geom::kHiOffset);
+  const int off_lo = Geom::lo(g, t, j), off_hi = off_lo + Geom::kHiOffset;
+  const uint2 lo = lds64(slice + (kSwz ? swizzle128(off_lo) : off_lo));
+  const uint2 hi = lds64(slice + (kSwz ? swizzle128(off_hi) : off_hi));
   split_hi_lo(lo.x, ah[0], al[0]);
   split_hi_lo(hi.x, ah[1], al[1]);
   split_hi_lo(lo.y, ah[2], al[2]);
@@ -185,6 +189,44 @@ __device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const 
       store4<OUT32>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
                     hb.d3 + lb.d3);
   }
+}
+
+// Variant of scan_step for rows that are chained over all eight steps, with
+// the running carry kept by fp32 adds instead of a dependent MMA: the totals of
+// this step come from MMAs with a zero accumulator, independent of every other
+// step, so consecutive steps overlap even with few warps per scheduler.
+struct RowCarry {
+  float h_lo, l_lo, h_hi, l_hi;  // (exact hi part, lo part) x (row g, row g+8)
+};
+
+template <int SC, bool OUT32>
+__device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah)[4],
+                                                      const uint32_t (&al)[4],
+                                                      const ScanOperands& ops, RowCarry& c,
+                                                      float xh, float xl, void* out,
+                                                      unsigned long long elem_base,
+                                                      int valid_elems, int g, int t) {
+  using Geom = ScanGeom<SC>;
+  const Acc zero{0.f, 0.f, 0.f, 0.f};
+  const Acc c_h{c.h_lo, c.h_lo, c.h_hi, c.h_hi}, c_l{c.l_lo, c.l_lo, c.l_hi, c.l_hi};
+  const Acc ha = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ua0, ops.ua1, c_h);
+  const Acc hb = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ub0, ops.ub1, c_h);
+  const Acc la = mma16816(al[0], al[1], al[2], al[3], ops.ua0, ops.ua1, c_l);
+  const Acc lb = mma16816(al[0], al[1], al[2], al[3], ops.ub0, ops.ub1, c_l);
+  if (j != 7) {
+    const Acc th = mma_ones(ah, zero), tl = mma_ones(al, zero);
+    c.h_lo += th.d0;
+    c.h_hi += th.d2;
+    c.l_lo += tl.d0;
+    c.l_hi += tl.d2;
+  }
+  const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
+  if (e_lo < valid_elems)
+    store4<OUT32>(out, elem_base + e_lo, (ha.d0 + xh) + (la.d0 + xl), (ha.d1 + xh) + (la.d1 + xl),
+                  (hb.d0 + xh) + (lb.d0 + xl), (hb.d1 + xh) + (lb.d1 + xl));
+  if (e_hi < valid_elems)
+    store4<OUT32>(out, elem_base + e_hi, (ha.d2 + xh) + (la.d2 + xl), (ha.d3 + xh) + (la.d3 + xl),
+                  (hb.d2 + xh) + (lb.d2 + xl), (hb.d3 + xh) + (lb.d3 + xl));
 }
 
 // Segment classes as for the reduction: 4..11 = 2^class elements (inside one

@@ -45,7 +45,7 @@ constexpr int kLookbackThreads      = (kConsumerWarps + 1 + kLookbackWarps) * 32
 // one float4 (row carries) per consumer lane, kept from pass 1 to pass 2
 constexpr int kCarryBytesPerStage   = kSaveCarries ? kConsumerWarps * 32 * 16 : 0;
 constexpr int kLookbackDynSmemBytes =
-    kLookbackStages * (kTileBytes + kCarryBytesPerStage) + 128;
+    kLookbackStages * (kTileBytes + kCarryBytesPerStage) + 1024;
 constexpr uint32_t kNoEnd = 0xffffffffu;
 constexpr unsigned long long kTileEnd = ~0ull;
 constexpr unsigned kStateAggregate = 1u, kStateInclusive = 2u;
@@ -129,9 +129,12 @@ __device__ __forceinline__ bool mbar_wait_or_stop(uint32_t bar, uint32_t parity,
   return false;
 }
 
-template <bool OUT32>
+// kSwz: tiles arrive through the tensor map `tmap` (2-D view {64, num_elems/64},
+// 128-byte swizzle; needs num_elems % 64 == 0), which makes the row-strided
+// 8-byte loads of both passes conflict-free; otherwise through linear copies.
+template <bool OUT32, bool kSwz>
 __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
-    scan_lookback_kernel(const ScanParams p) {
+    scan_lookback_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tmap) {
   constexpr int SC = 15;  // row-stream geometry, rows always chained
   constexpr int NS = kLookbackStages;
   extern __shared__ uint8_t dyn_smem[];
@@ -141,7 +144,8 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   __shared__ double tile_excl[NS];                 // exclusive prefix of the tile in its segment
   __shared__ uint32_t s_abort, s_end_index;
 
-  uint8_t* ring = dyn_smem + ((128u - (smem_u32(dyn_smem) & 127u)) & 127u);
+  // 1 KiB-aligned ring: the swizzle pattern repeats every 1024 bytes
+  uint8_t* ring = dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u);
   float4* carries = reinterpret_cast<float4*>(ring + NS * kTileBytes);  // [NS][8][32]
   const uint32_t ring_u32 = smem_u32(ring);
   const uint32_t full0 = smem_u32(&bars[0]), p1done0 = smem_u32(&bars[NS]),
@@ -182,8 +186,14 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
         const unsigned long long off = tile * kTileBytes;
         const unsigned long long rem = total_bytes - off;
         const uint32_t bytes = rem < (unsigned long long)kTileBytes ? (uint32_t)rem : kTileBytes;
-        mbar_arrive_expect_tx(full0 + 8 * s, bytes);
-        tma_load_1d(ring_u32 + s * kTileBytes, p.in + off, bytes, full0 + 8 * s);
+        if constexpr (kSwz) {
+          // the whole box always arrives: rows past the end of the array come as zeros
+          mbar_arrive_expect_tx(full0 + 8 * s, kTileBytes);
+          tma_load_2d(ring_u32 + s * kTileBytes, &tmap, 0, (int)(tile * kTileRows), full0 + 8 * s);
+        } else {
+          mbar_arrive_expect_tx(full0 + 8 * s, bytes);
+          tma_load_1d(ring_u32 + s * kTileBytes, p.in + off, bytes, full0 + 8 * s);
+        }
       }
     }
     return;
@@ -273,13 +283,14 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     }
     const SliceView v = slice_view(s, tile);
     const bool active = v.valid_bytes > 0;
-    if (active && v.valid_bytes < kSliceBytes) zero_slice_tail(v.slice, v.valid_bytes, lane);
+    if constexpr (!kSwz)
+      if (active && v.valid_bytes < kSliceBytes) zero_slice_tail(v.slice, v.valid_bytes, lane);
     Acc tot_h = zero, tot_l = zero;
     if (active) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
-        load_split<Geom>(v.slice, g, t, j, ah, al);
+        load_split<Geom, kSwz>(v.slice, g, t, j, ah, al);
         tot_h = mma_ones(ah, tot_h);
         tot_l = mma_ones(al, tot_l);
       }
@@ -314,21 +325,22 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint32_t ah[4], al[4];
-          load_split<Geom>(v.slice, g, t, j, ah, al);
+          load_split<Geom, kSwz>(v.slice, g, t, j, ah, al);
           tot_h = mma_ones(ah, tot_h);
           tot_l = mma_ones(al, tot_l);
         }
         float slice_h, slice_l;
         row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
       }
+      RowCarry rc{ch_lo, cl_lo, ch_hi, cl_hi};
       const unsigned long long elem_base = v.slice_off / 2;
       const int valid_elems = v.valid_bytes / 2;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
-        load_split<Geom>(v.slice, g, t, j, ah, al);
-        scan_step<SC, OUT32, true>(j, ah, al, ops, ch_lo, cl_lo, ch_hi, cl_hi, xh, xl, p.out,
-                                   elem_base, valid_elems, g, t);
+        load_split<Geom, kSwz>(v.slice, g, t, j, ah, al);
+        scan_step_independent<SC, OUT32>(j, ah, al, ops, rc, xh, xl, p.out, elem_base, valid_elems,
+                                         g, t);
       }
     }
     __syncwarp();
