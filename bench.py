@@ -66,14 +66,12 @@ def hbm_peak():
 
 
 class ClockSampler:
-    """SM clock and throttle reasons of one GPU, read through NVML every few milliseconds
-    while the timed region runs (read-only queries; nothing is set)."""
+    """SM clock and throttle reasons of one GPU through NVML (read-only queries; nothing is
+    set).  sample() is called by the benchmark while it waits for the timed region to finish,
+    so every sample is taken under load."""
 
-    def __init__(self, index: int, period_s: float = 0.002):
-        import threading
+    def __init__(self, index: int):
         self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -83,42 +81,41 @@ class ClockSampler:
                 ids = [v.strip() for v in visible.split(",") if v.strip()]
                 if index < len(ids) and ids[index].isdigit():
                     phys = int(ids[index])
-            self._nvml = pynvml
+            self._n = pynvml
             self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            self._get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self._bits = {
+                "hw_slowdown": getattr(pynvml, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(pynvml, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(pynvml, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(pynvml, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            }
         except Exception as e:  # no NVML: report that instead of a number
-            self._nvml = None
+            self._n = None
             self.reasons.add(f"nvml unavailable: {type(e).__name__}")
+
+    def sample(self):
+        if self._n is None:
             return
-        self._period = period_s
-        self._thread = threading.Thread(target=self._run, daemon=True)
-        self._thread.start()
+        try:
+            self.samples.append(self._n.nvmlDeviceGetClockInfo(self._h, self._n.NVML_CLOCK_SM))
+            r = self._get_reasons(self._h)
+            for name, bit in self._bits.items():
+                if r & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
 
-    def _run(self):
-        n = self._nvml
-        bits = {
-            "hw_slowdown": getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8),
-            "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
-            "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
-            "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4),
-        }
-        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
-            n.nvmlDeviceGetCurrentClocksThrottleReasons
-        while not self._stop.is_set():
-            try:
-                self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
-                r = get_reasons(self._h)
-                for name, bit in bits.items():
-                    if r & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            self._stop.wait(self._period)
+    def wait_for(self, event):
+        """Sample until the CUDA event has completed (the GPU is busy with the timed steps)."""
+        self.sample()
+        while not event.query():
+            self.sample()
+            time.sleep(0.0002)
 
-    def stop(self):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join(timeout=2)
+    def result(self):
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
                 "sm_max_mhz": self.max_mhz, "samples": len(self.samples),
                 "reasons": sorted(self.reasons)}
@@ -147,7 +144,7 @@ def cpu_sweep(log2_sample: int, min_seconds: float, max_passes: int):
     return passes * len(SWEEP) * n / dt / 1e9, cores, passes, dt
 
 
-def run_reference_arm(args, rank: int):
+def run_reference_arm(args, rank: int, json_fd: int):
     """The CPU implementation of the sweep, all host threads, rank 0 only."""
     if rank != 0:
         return
@@ -172,7 +169,7 @@ def run_reference_arm(args, rank: int):
     dt = time.perf_counter() - t0
     value = args.steps * len(SWEEP) * n / dt / 1e9
     sample = f"{len(SWEEP)} segment sizes x 2^{log2_sample} elements per step"
-    print(json.dumps({
+    emit(json_fd, {
         "impl": "reference", "metric": "segmented_reduce_sweep_throughput", "value": value,
         "unit": "Gelem/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -183,7 +180,7 @@ def run_reference_arm(args, rank: int):
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }))
+    })
 
 
 def workload_config(args, world: int):
@@ -253,11 +250,11 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
     def gelem(n, ms):
         return n / (ms * 1e-3) / 1e9
 
-    def entry(n, bytes_per_elem, ms_med, ms_min):
-        g = gelem(n, ms_med)
+    def entry(n, bytes_per_elem, ms_med, ms_min, gpus=1):
+        g = gelem(n, ms_med)  # n = elements over all `gpus` GPUs; hbm_frac is per GPU
         return {"gelem_per_s": round(g, 1), "gelem_per_s_best": round(gelem(n, ms_min), 1),
                 "gbytes_per_s": round(g * bytes_per_elem, 1),
-                "hbm_frac": round(g * bytes_per_elem / peak_gbs, 4), "ms": round(ms_med, 4)}
+                "hbm_frac": round(g * bytes_per_elem / peak_gbs / gpus, 4), "ms": round(ms_med, 4)}
 
     # C1: 2^24 elements, S=16, cold cache: rotate over 8 buffer sets (256 MiB of input > 2x L2)
     n24 = 1 << 24
@@ -308,7 +305,7 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
         t = torch.tensor([ms_med, ms_min], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_med, ms_min = t.tolist()
-    out["C4_full_reduce_2^30_per_gpu"] = entry(n30 * world, 2, ms_med, ms_min)
+    out["C4_full_reduce_2^30_per_gpu"] = entry(n30 * world, 2, ms_med, ms_min, world)
 
     o = torch.empty(n30, dtype=torch.float32, device=dev)
 
@@ -323,7 +320,7 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
         t = torch.tensor([ms_med, ms_min], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_med, ms_min = t.tolist()
-    out["C5_full_scan_2^30_per_gpu_f32"] = entry(n30 * world, 6, ms_med, ms_min)
+    out["C5_full_scan_2^30_per_gpu_f32"] = entry(n30 * world, 6, ms_med, ms_min, world)
     return out
 
 
@@ -380,9 +377,8 @@ def run_e2e(torch, tcu, dist, args, rank, world):
     ctx = tcu.HostContext(chunk_elements=1 << 25)
     steps = max(2, min(args.steps, 5))
 
-    def step():
-        for s in SWEEP:
-            ctx.run(tcu.OP_SEGMENTED_REDUCE, h_in, h_out[s], s, algo=args.algo)
+    def step():  # one call: every chunk is uploaded once and reduced at all six segment sizes
+        ctx.reduce_sweep(h_in, SWEEP, [h_out[s] for s in SWEEP], algo=args.algo)
 
     step()
     torch.cuda.synchronize()
@@ -397,7 +393,7 @@ def run_e2e(torch, tcu, dist, args, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t[0])
     ctx.close()
-    h2d = len(SWEEP) * n * 2
+    h2d = n * 2
     d2h = sum(n // s * 4 for s in SWEEP)
     # spot check: the results that came back are the right ones
     import oracle
@@ -405,10 +401,11 @@ def run_e2e(torch, tcu, dist, args, rank, world):
     assert np.array_equal(h_out[1024][:1 << 10].numpy(), ref.astype(np.float32))
     return {"value": steps * len(SWEEP) * n * world / dt / 1e9, "unit": "Gelem/s",
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
-            "note": "pinned host buffers, chunked copies overlapped with kernels on two streams"}
+            "note": "tcu_host_segmented_reduce_sweep_f16: pinned host buffers, each 64 MiB chunk "
+                    "copied once and reduced at all six sizes, copies overlap kernels on two streams"}
 
 
-def profile_pass(torch, tcu, args, n):
+def profile_pass(torch, tcu, args, n, json_fd):
     """One launch of each kernel of a family, for a profiler to capture."""
     x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024, 0)
     if args.profile == "reduce":
@@ -423,16 +420,35 @@ def profile_pass(torch, tcu, args, n):
         tcu.full_scan(x, out_dtype=torch.float32)
     torch.cuda.synchronize()
     assert tcu.device_error() == 0
-    print(json.dumps({"profile": args.profile, "log2_elems": args.log2_elems, "algo": args.algo}))
+    emit(json_fd, {"profile": args.profile, "log2_elems": args.log2_elems, "algo": args.algo})
 
 
 def main():
     args = parse_args()
+    # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line
+    # there.  Everything else goes to stderr: fd 1 is pointed at fd 2 for the run and the result
+    # is written to the saved descriptor at the end.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        _main(args, json_fd)
+    finally:
+        sys.stdout.flush()
+        os.dup2(json_fd, 1)
+        os.close(json_fd)
+
+
+def emit(json_fd: int, obj) -> None:
+    os.write(json_fd, (json.dumps(obj) + "\n").encode())
+
+
+def _main(args, json_fd):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
-        run_reference_arm(args, rank)
+        run_reference_arm(args, rank, json_fd)
         return
 
     import torch
@@ -452,7 +468,7 @@ def main():
     dev = torch.device("cuda")
     peak_gbs, peak_kind = hbm_peak()
     if args.profile:
-        profile_pass(torch, tcu, args, n)
+        profile_pass(torch, tcu, args, n, json_fd)
         return
 
     # this rank's shard of the logical array: elements [rank*n, (rank+1)*n), two buffers to rotate
@@ -504,8 +520,10 @@ def main():
     for k in range(args.steps):
         run_step()
     t_end.record()
+    if sampler:
+        sampler.wait_for(t_end)
     torch.cuda.synchronize()
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.result() if sampler else None
     if world > 1:
         dist.barrier()
     total_ms = t_begin.elapsed_time(t_end)
@@ -569,7 +587,7 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(result))
+        emit(json_fd, result)
 
 
 if __name__ == "__main__":

@@ -175,6 +175,19 @@ void tcu_host_ctx_destroy(tcu_host_ctx* ctx);
 int tcu_host_run_f16(tcu_host_ctx* ctx, int op, const void* h_in, void* h_out, int out_type,
                      size_t num_elements, size_t segment_size, int algo);
 
+/*
+ * The reference's segment-size sweep (one array, many segment sizes:
+ * SEG_16_ARGS ... SEG_16384_ARGS over the same element counts,
+ * src/reduction/args.hpp:64-75) for an array in HOST memory: every chunk is
+ * copied to the device once and reduced at all num_sizes segment sizes while
+ * the next chunk is on its way; h_outs[i] receives num_elements /
+ * segment_sizes[i] sums.  Saves num_sizes - 1 of num_sizes host-to-device
+ * passes compared with num_sizes calls of tcu_host_run_f16.
+ */
+int tcu_host_segmented_reduce_sweep_f16(tcu_host_ctx* ctx, const void* h_in, size_t num_elements,
+                                        int num_sizes, const size_t* segment_sizes,
+                                        void* const* h_outs, int out_type, int algo);
+
 /* Reads (and optionally clears) the device-side error word of the current
  * device: bit 0 = an mbarrier wait ran out, bit 1 = a tile-status poll ran
  * out.  Synchronises the device.  Returns TCU_ERR_TIMEOUT if any bit is set. */

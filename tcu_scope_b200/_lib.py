@@ -34,6 +34,9 @@ SIGNATURES = {
     "tcu_host_ctx_destroy": (None, [c_void_p]),
     "tcu_host_run_f16": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t,
                                  c_int]),
+    "tcu_host_segmented_reduce_sweep_f16": (c_int, [c_void_p, c_void_p, c_size_t, c_int,
+                                                    ctypes.POINTER(c_size_t),
+                                                    ctypes.POINTER(c_void_p), c_int, c_int]),
     "tcu_device_error": (c_int, [ctypes.POINTER(ctypes.c_uint), c_int]),
     "tcu_tile_elements": (c_int, []),
     "tcu_num_sms": (c_int, []),

@@ -170,4 +170,60 @@ int tcu_host_run_f16(tcu_host_ctx* c, int op, const void* h_in, void* h_out, int
   return TCU_OK;
 }
 
+int tcu_host_segmented_reduce_sweep_f16(tcu_host_ctx* c, const void* h_in, size_t num_elements,
+                                        int num_sizes, const size_t* segment_sizes,
+                                        void* const* h_outs, int out_type, int algo) {
+  if (!c || !h_in || !segment_sizes || !h_outs || num_sizes <= 0 || num_sizes > 32)
+    return TCU_ERR_INVALID_ARG;
+  if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
+  if (num_elements == 0) return TCU_OK;
+  size_t max_seg = 0;
+  for (int i = 0; i < num_sizes; ++i) {
+    if (!h_outs[i]) return TCU_ERR_INVALID_ARG;
+    if (segment_class(segment_sizes[i]) < 0) return TCU_ERR_UNSUPPORTED;
+    if (num_elements % segment_sizes[i] != 0) return TCU_ERR_INVALID_ARG;
+    if (segment_sizes[i] > max_seg) max_seg = segment_sizes[i];
+  }
+  if (max_seg > c->chunk_elems) return TCU_ERR_UNSUPPORTED;
+  // sizes are powers of two: a multiple of the largest is a multiple of all
+  const size_t chunk    = c->chunk_elems / max_seg * max_seg;
+  const size_t out_elem = out_type == TCU_OUT_F32 ? 4 : 2;
+  // all outputs of one chunk share the staging buffer (chunk * 4 bytes): with every
+  // size >= 16 and at most 32 sizes they need at most 32 * chunk/16 * 4 bytes -- check anyway
+  size_t need = 0;
+  for (int i = 0; i < num_sizes; ++i) need += (chunk / segment_sizes[i] * out_elem + 255) / 256 * 256;
+  if (need > c->chunk_elems * 4) return TCU_ERR_UNSUPPORTED;
+  const uint8_t* src = static_cast<const uint8_t*>(h_in);
+  const size_t num_chunks = (num_elements + chunk - 1) / chunk;
+  int status = TCU_OK;
+  for (size_t ci = 0; ci < num_chunks && status == TCU_OK; ++ci) {
+    const int k        = int(ci & 1);
+    const size_t first = ci * chunk;
+    const size_t elems = num_elements - first < chunk ? num_elements - first : chunk;
+    cudaStream_t st    = c->st[k];
+    if (cudaMemcpyAsync(c->d_in[k], src + first * 2, elems * 2, cudaMemcpyHostToDevice, st) !=
+        cudaSuccess) {
+      status = TCU_ERR_CUDA;
+      break;
+    }
+    size_t off = 0;
+    for (int i = 0; i < num_sizes && status == TCU_OK; ++i) {
+      const size_t s = segment_sizes[i], segs = elems / s;
+      uint8_t* d_out = static_cast<uint8_t*>(c->d_out[k]) + off;
+      status = tcu_segmented_reduce_f16(c->d_in[k], d_out, out_type, segs, s, algo, c->d_ws[k],
+                                        c->ws_bytes, st);
+      if (status == TCU_OK &&
+          cudaMemcpyAsync(static_cast<uint8_t*>(h_outs[i]) + first / s * out_elem, d_out,
+                          segs * out_elem, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+        status = TCU_ERR_CUDA;
+      off += (chunk / s * out_elem + 255) / 256 * 256;
+    }
+  }
+  const bool s0 = cudaStreamSynchronize(c->st[0]) == cudaSuccess;
+  const bool s1 = cudaStreamSynchronize(c->st[1]) == cudaSuccess;
+  if (status != TCU_OK) return status;
+  return s0 && s1 ? TCU_OK : TCU_ERR_CUDA;
+}
+
+
 }  // extern "C"

@@ -171,6 +171,27 @@ class HostContext:
         except Exception:
             pass
 
+    def reduce_sweep(self, h_in: torch.Tensor, segment_sizes, h_outs, algo="auto"):
+        """Segmented reductions of one host array at several segment sizes; each chunk of the
+        input crosses the bus once.  h_outs[i]: host tensor of h_in.numel() // segment_sizes[i]."""
+        if h_in.is_cuda or h_in.dtype != torch.float16 or not h_in.is_contiguous():
+            raise TypeError("h_in must be a contiguous float16 host tensor")
+        k = len(segment_sizes)
+        if k != len(h_outs) or k == 0:
+            raise ValueError("one output per segment size")
+        code = _out_code(h_outs[0].dtype)
+        for s, o in zip(segment_sizes, h_outs):
+            if o.is_cuda or not o.is_contiguous() or _out_code(o.dtype) != code:
+                raise TypeError("outputs must be contiguous host tensors of one dtype")
+            if o.numel() * s != h_in.numel():
+                raise ValueError("output size does not match num_elements / segment_size")
+        sizes = (ctypes.c_size_t * k)(*segment_sizes)
+        outs = (ctypes.c_void_p * k)(*[o.data_ptr() for o in h_outs])
+        _check(_lib.load().tcu_host_segmented_reduce_sweep_f16(
+            self._ctx, h_in.data_ptr(), h_in.numel(), k, sizes, outs, code, ALGO[algo]),
+            "tcu_host_segmented_reduce_sweep_f16")
+        return h_outs
+
     def run(self, op: int, h_in: torch.Tensor, h_out: torch.Tensor, segment_size: int = 0,
             algo="auto") -> torch.Tensor:
         if h_in.is_cuda or h_out.is_cuda:

@@ -280,6 +280,15 @@ def test_host_buffers_match_device_path(tcu):
     out = torch.empty(n // 256, dtype=torch.float32).pin_memory()
     ctx.run(tcu.OP_SEGMENTED_REDUCE, h_in, out, 256)
     assert np.array_equal(out.numpy(), oracle.np_segmented_reduce(xb, 256).astype(np.float32))
+    sizes = [16, 256, 16384]
+    outs = [torch.empty(n // s, dtype=torch.float32).pin_memory() for s in sizes]
+    ctx.reduce_sweep(h_in, sizes, outs)
+    for s, o in zip(sizes, outs):
+        want = oracle.np_segmented_reduce(xb, s)
+        if s >= 256:
+            assert np.array_equal(o.numpy(), want.astype(np.float32))
+        else:
+            assert oracle.np_check_f32(o.numpy(), want)[0] == 0
     sc = torch.empty(n, dtype=torch.float16).pin_memory()
     ctx.run(tcu.OP_SEGMENTED_SCAN, h_in, sc, 4096)
     assert oracle.np_check_f16(sc.view(torch.int16).numpy().view(np.uint16),
