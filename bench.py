@@ -365,6 +365,55 @@ def reference_kernels_leg(torch, tcu, args):
     return out
 
 
+def cub_leg(torch, tcu, args):
+    """Baseline leg: CUB device-wide primitives (the CUDA toolkit's CCCL) on the same inputs --
+    the library comparison the reference itself makes.  None when oracle/libtcu_cub.so is missing."""
+    import ctypes
+    import oracle
+    cub = oracle.cub_lib()
+    if cub is None:
+        return None
+    stream = torch.cuda.current_stream().cuda_stream
+    n28 = 1 << min(args.log2_elems, 28)
+    n30 = 1 << min(args.log2_elems + 2, 30)
+    out = {"unit": "Gelem/s", "seg_reduce_f32": {}, "seg_scan": {}}
+
+    def timed(op, x, o, n, seg, reps):
+        need = ctypes.c_size_t(oracle.cub_temp_bytes(op, n, seg))
+        tmp = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+
+        def call():
+            rc = cub.tcu_cub_run(op, x.data_ptr(), o.data_ptr(), n, seg, tmp.data_ptr(),
+                                 ctypes.byref(need), stream)
+            assert rc == 0, rc
+        ms, _ = time_op(torch, call, reps, 2)
+        return round(n / ms / 1e6, 1)
+
+    x = tcu.fill(torch.empty(n28, dtype=torch.float16, device="cuda"), 2024, 0)
+    total_ms = 0.0
+    for s in SWEEP:
+        o = torch.empty(n28 // s, dtype=torch.float32, device="cuda")
+        g = timed(oracle.CUB_SEG_REDUCE, x, o, n28, s, 3 if s < 64 else 5)
+        out["seg_reduce_f32"][str(s)] = g
+        total_ms += n28 / g / 1e6
+    out["seg_reduce_sweep"] = round(len(SWEEP) * n28 / total_ms / 1e6, 1)
+    o16 = torch.empty(n28, dtype=torch.float16, device="cuda")
+    for s in (16, 256):
+        out["seg_scan"][f"{s}_f16"] = timed(oracle.CUB_SEG_SCAN_F16, x, o16, n28, s, 5)
+    del o16
+    o32 = torch.empty(n28, dtype=torch.float32, device="cuda")
+    out["seg_scan"]["4096_f32"] = timed(oracle.CUB_SEG_SCAN_F32, x, o32, n28, 4096, 5)
+    del o32, x
+    x = tcu.fill(torch.empty(n30, dtype=torch.float16, device="cuda"), 3, 0, "uniform_01")
+    o1 = torch.empty(1, dtype=torch.float32, device="cuda")
+    out["full_reduce"] = timed(oracle.CUB_FULL_REDUCE, x, o1, n30, n30, 5)
+    o = torch.empty(n30, dtype=torch.float32, device="cuda")
+    out["full_scan_f32"] = timed(oracle.CUB_FULL_SCAN, x, o, n30, n30, 5)
+    out["note"] = ("cub::DeviceSegmentedReduce / DeviceScan::InclusiveSumByKey / DeviceReduce / "
+                   "DeviceScan, fp16 inputs widened to fp32 by a transform iterator")
+    return out
+
+
 def run_e2e(torch, tcu, dist, args, rank, world):
     """Same sweep through the host-buffer entry point: pinned host input, results read back."""
     import numpy as np
@@ -583,6 +632,9 @@ def _main(args, json_fd):
             rk = reference_kernels_leg(torch, tcu, args)
             if rk is not None:
                 result["reference_kernels_on_this_gpu"] = rk
+            cb = cub_leg(torch, tcu, args)
+            if cb is not None:
+                result["cub_on_this_gpu"] = cb
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

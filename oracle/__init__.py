@@ -221,3 +221,34 @@ def ref_lib():
         fn.restype, fn.argtypes = i32, [vp, vp, sz, sz, i32, i32, vp]
     _ref = lib
     return lib
+
+
+# ---------------------------------------------------------- CUB library baseline
+CUB_LIB_PATH = os.path.join(HERE, "libtcu_cub.so")
+_cub = None
+
+
+def cub_lib():
+    """oracle/libtcu_cub.so (``make -C oracle cub``): CUB device-wide reduce / scan on the same
+    inputs, the library baseline.  None when it has not been built."""
+    global _cub
+    if _cub is not None:
+        return _cub
+    if not os.path.exists(CUB_LIB_PATH):
+        return None
+    lib = ctypes.CDLL(CUB_LIB_PATH)
+    vp, sz, i32 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    lib.tcu_cub_run.restype = i32
+    lib.tcu_cub_run.argtypes = [i32, vp, vp, sz, sz, vp, ctypes.POINTER(sz), vp]
+    _cub = lib
+    return lib
+
+
+CUB_FULL_REDUCE, CUB_SEG_REDUCE, CUB_FULL_SCAN, CUB_SEG_SCAN_F32, CUB_SEG_SCAN_F16 = range(5)
+
+
+def cub_temp_bytes(op: int, n: int, segment_size: int) -> int:
+    need = ctypes.c_size_t(0)
+    rc = cub_lib().tcu_cub_run(op, None, None, n, segment_size, None, ctypes.byref(need), None)
+    assert rc == 0, rc
+    return max(int(need.value), 1)
