@@ -100,9 +100,10 @@ cudaError_t launch_reduce(const ReduceParams& p, int grid, cudaStream_t st) {
 template <int SC, bool OUT32>
 cudaError_t launch_scan(const ScanParams& p, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
-  cudaError_t e = ensure_smem(seg_scan_kernel<SC, OUT32>, configured, kDynSmemBytes);
+  cudaError_t e = ensure_smem(seg_scan_kernel<SC, OUT32>, configured, scan_dyn_smem_bytes(SC));
   if (e != cudaSuccess) return e;
-  seg_scan_kernel<SC, OUT32><<<grid, kThreads, kDynSmemBytes, st>>>(p);
+  seg_scan_kernel<SC, OUT32>
+      <<<grid * scan_ctas_per_sm(SC), kThreads, scan_dyn_smem_bytes(SC), st>>>(p);
   return cudaGetLastError();
 }
 

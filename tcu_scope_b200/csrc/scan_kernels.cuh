@@ -77,7 +77,10 @@ __device__ __forceinline__ void store4(void* out, unsigned long long idx, float 
 // at step j (row g+8 is kHiOffset further).
 template <int SC>
 struct ScanGeom {
-  static constexpr bool kLinear   = SC == 4;
+#ifndef TCU_S16_LINEAR
+#define TCU_S16_LINEAR 1
+#endif
+  static constexpr bool kLinear   = SC == 4 && TCU_S16_LINEAR != 0;
   static constexpr int kHiOffset  = kLinear ? 256 : 2048;
   __device__ static __forceinline__ int lo(int g, int t, int j) {
     return kLinear ? 512 * j + 32 * g + 8 * t : 256 * g + 32 * j + 8 * t;
@@ -231,9 +234,23 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
 
 // Segment classes as for the reduction: 4..11 = 2^class elements (inside one
 // slice), 12..14 = 4096/8192/16384 (2/4/8 slices of one tile).
+// Launch shape per class.  Classes up to 128 elements make one pass over the
+// slice and need few registers: two CTAs per SM (3-stage rings) double the
+// warps each scheduler can interleave, which is worth 5-9 % there.  From 256
+// elements on the slice is read once and kept in registers between the row
+// totals and the scan proper, which only fits with one CTA per SM.
+#ifndef TCU_SCAN_2CTA_MAX_CLASS
+#define TCU_SCAN_2CTA_MAX_CLASS 7
+#endif
+__host__ __device__ constexpr int scan_ctas_per_sm(int sc) { return sc <= TCU_SCAN_2CTA_MAX_CLASS ? 2 : 1; }
+__host__ __device__ constexpr int scan_stages(int sc) { return scan_ctas_per_sm(sc) == 1 ? kStages : 3; }
+__host__ __device__ constexpr int scan_dyn_smem_bytes(int sc) { return scan_stages(sc) * kTileBytes + 128; }
+
 template <int SC, bool OUT32>
-__global__ void __launch_bounds__(kThreads, 1) seg_scan_kernel(const ScanParams p) {
+__global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kernel(const ScanParams p) {
   static_assert(SC >= 4 && SC <= 14, "the look-back class has its own kernel");
+  constexpr int kStages = scan_stages(SC);  // shadows the library-wide ring depth
+  constexpr bool kScanCache = scan_ctas_per_sm(SC) == 1;  // slice kept in registers between passes
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kStages];
   __shared__ float2 part[2][kConsumerWarps];
@@ -291,20 +308,23 @@ __global__ void __launch_bounds__(kThreads, 1) seg_scan_kernel(const ScanParams 
     if (active && valid_bytes < kSliceBytes) zero_slice_tail(slice, valid_bytes, lane);
 
     // ---- load + split the whole slice; row totals for classes that chain rows
-    uint32_t ah[8][4], al[8][4];
+    constexpr int kKeep = kScanCache ? 8 : 1;
+    uint32_t ah[kKeep][4], al[kKeep][4];
     Acc tot_h = zero, tot_l = zero;
-    if (active) {
+    if (active && (kScanCache || SC >= 8)) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        load_split<Geom>(slice, g, t, j, ah[j], al[j]);
+        load_split<Geom>(slice, g, t, j, ah[kScanCache ? j : 0], al[kScanCache ? j : 0]);
         if constexpr (SC >= 8) {
-          tot_h = mma_ones(ah[j], tot_h);
-          tot_l = mma_ones(al[j], tot_l);
+          tot_h = mma_ones(ah[kScanCache ? j : 0], tot_h);
+          tot_l = mma_ones(al[kScanCache ? j : 0], tot_l);
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty0 + 8 * s);  // everything needed is in registers
+    if constexpr (kScanCache) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);  // everything needed is in registers
+    }
 
     // ---- carries into each MMA row, and from the earlier slices of the segment
     float ch_lo = 0.f, cl_lo = 0.f, ch_hi = 0.f, cl_hi = 0.f;
@@ -326,14 +346,21 @@ __global__ void __launch_bounds__(kThreads, 1) seg_scan_kernel(const ScanParams 
         }
       }
     }
-    if (!active) continue;
-
-    const unsigned long long elem_base = slice_off / 2;
-    const int valid_elems = valid_bytes / 2;
+    if (active) {
+      const unsigned long long elem_base = slice_off / 2;
+      const int valid_elems = valid_bytes / 2;
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      scan_step<SC, OUT32, (SC >= 12)>(j, ah[j], al[j], ops, ch_lo, cl_lo, ch_hi, cl_hi, xh, xl,
-                                       p.out, elem_base, valid_elems, g, t);
+      for (int j = 0; j < 8; ++j) {
+        if constexpr (!kScanCache) load_split<Geom>(slice, g, t, j, ah[0], al[0]);  // second read
+        scan_step<SC, OUT32, (SC >= 12)>(j, ah[kScanCache ? j : 0], al[kScanCache ? j : 0], ops, ch_lo,
+                                         cl_lo, ch_hi, cl_hi, xh, xl, p.out, elem_base, valid_elems,
+                                         g, t);
+      }
+    }
+    if constexpr (!kScanCache) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
   }
 }
 

@@ -41,12 +41,36 @@ constexpr bool kSaveCarries         = TCU_LB_SAVE_CARRIES != 0;
 constexpr int kLookahead            = TCU_LOOKAHEAD;  // pass 1 runs this many tiles ahead of pass 2
 constexpr int kLookbackWarps        = 4;
 constexpr int kLookbackCtasPerSm    = 1;
-constexpr int kLookbackThreads      = (kConsumerWarps + 1 + kLookbackWarps) * 32;
+// Warp roles: [0,8) pass-1 warps, [8,16) pass-2 warps, 16 producer, 17.. look-back.
+// Pass 1 and pass 2 of different tiles run at the same time on different warps:
+// twice the warps to interleave on each scheduler, which is what the dependent
+// MMA / shuffle chains of the two passes need to keep the issue slots busy.
+constexpr int kPass2Warp0           = kConsumerWarps;
+constexpr int kProducerWarp         = 2 * kConsumerWarps;
+constexpr int kLookbackWarp0        = kProducerWarp + 1;
+constexpr int kLookbackThreads      = (2 * kConsumerWarps + 1 + kLookbackWarps) * 32;
 // one float4 (row carries) per consumer lane, kept from pass 1 to pass 2
 constexpr int kCarryBytesPerStage   = kSaveCarries ? kConsumerWarps * 32 * 16 : 0;
 constexpr int kLookbackDynSmemBytes =
     kLookbackStages * (kTileBytes + kCarryBytesPerStage) + 1024;
 constexpr uint32_t kNoEnd = 0xffffffffu;
+
+#ifdef TCU_LB_PROFILE
+// debug counters (ns): [0] look-back time sum [1] tiles [2] look-back max
+// [3] pass-2 warp 8 wait for resolved  [4] pass-1 warp 0 wait for full  [5] pass-1 compute
+// [6] pass-2 compute  [7] producer wait for empty
+__device__ unsigned long long g_lb_stats[8];
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define LB_T0() const unsigned long long lb_t0 = gtime()
+#define LB_ADD(slot, cond) do { if (cond) atomicAdd(&g_lb_stats[slot], gtime() - lb_t0); } while (0)
+#else
+#define LB_T0()
+#define LB_ADD(slot, cond)
+#endif
 constexpr unsigned long long kTileEnd = ~0ull;
 constexpr unsigned kStateAggregate = 1u, kStateInclusive = 2u;
 constexpr unsigned long long kBlockTiles = 32;  // tiles per second-level status word
@@ -170,12 +194,16 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   const unsigned long long total_bytes = p.num_elems * 2ull;
   const unsigned long long num_tiles   = (total_bytes + kTileBytes - 1) / kTileBytes;
 
-  if (warp == kConsumerWarps) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       for (uint32_t i = 0;; ++i) {
         const uint32_t s = i % NS, ph = (i / NS) & 1u;
-        if (!mbar_wait_or_stop(empty0 + 8 * s, ph ^ 1u, abort_flag, nullptr, 0)) break;
+        {
+          LB_T0();
+          if (!mbar_wait_or_stop(empty0 + 8 * s, ph ^ 1u, abort_flag, nullptr, 0)) break;
+          LB_ADD(7, true);
+        }
         const unsigned long long tile = atomicAdd(p.ticket, 1u);
         if (tile >= num_tiles) {
           stage_tile[s] = kTileEnd;
@@ -199,12 +227,13 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     return;
   }
 
-  if (warp > kConsumerWarps) {
+  if (warp >= kLookbackWarp0) {
     // ------------------------------------------------------ look-back warps
-    for (uint32_t i = warp - kConsumerWarps - 1;; i += kLookbackWarps) {
+    for (uint32_t i = warp - kLookbackWarp0;; i += kLookbackWarps) {
       const uint32_t s = i % NS, ph = (i / NS) & 1u;
       if (!mbar_wait_or_stop(p1done0 + 8 * s, ph, abort_flag, end_index, i)) break;
       const unsigned long long tile = stage_tile[s];
+      LB_T0();
       double agg = 0.0;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) agg += (double)part[s][w].x + (double)part[s][w].y;
@@ -247,6 +276,12 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       if (lane == 0) {
         tile_excl[s] = excl;
         mbar_arrive(resolved0 + 8 * s);  // release: tile_excl is visible to the waiters
+#ifdef TCU_LB_PROFILE
+        const unsigned long long dt = gtime() - lb_t0;
+        atomicAdd(&g_lb_stats[0], dt);
+        atomicAdd(&g_lb_stats[1], 1ull);
+        atomicMax(&g_lb_stats[2], dt);
+#endif
       }
     }
     return;
@@ -254,6 +289,7 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
 
   // --------------------------------------------------------------- consumers
   using Geom = ScanGeom<SC>;
+  const int cw = warp & (kConsumerWarps - 1);  // the slice this warp owns, in either pass
   const int g = lane >> 2, t = lane & 3;
   const ScanOperands ops = make_scan_operands(lane);
   const Acc zero{0.f, 0.f, 0.f, 0.f};
@@ -265,8 +301,8 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   };
   auto slice_view = [&](uint32_t s, unsigned long long tile) {
     SliceView v;
-    v.slice     = ring + s * kTileBytes + warp * kSliceBytes;
-    v.slice_off = tile * kTileBytes + (unsigned long long)warp * kSliceBytes;
+    v.slice     = ring + s * kTileBytes + cw * kSliceBytes;
+    v.slice_off = tile * kTileBytes + (unsigned long long)cw * kSliceBytes;
     const long long left = (long long)total_bytes - (long long)v.slice_off;
     v.valid_bytes = left <= 0 ? 0 : (left < kSliceBytes ? (int)left : kSliceBytes);
     return v;
@@ -275,7 +311,12 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   // pass 1 of local tile i: slice total and row carries.  false = no such tile.
   auto pass1 = [&](uint32_t i) -> bool {
     const uint32_t s = i % NS, ph = (i / NS) & 1u;
-    if (!mbar_wait_or_stop(full0 + 8 * s, ph, abort_flag, nullptr, 0)) return false;
+    {
+      LB_T0();
+      if (!mbar_wait_or_stop(full0 + 8 * s, ph, abort_flag, nullptr, 0)) return false;
+      LB_ADD(4, threadIdx.x == 0);
+    }
+    LB_T0();
     const unsigned long long tile = stage_tile[s];
     if (tile == kTileEnd) {
       if (lane == 0) *end_index = i;  // lets the look-back warps leave
@@ -298,27 +339,36 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     float ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l;
     row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
     if constexpr (kSaveCarries)
-      carries[(s * kConsumerWarps + warp) * 32 + lane] = make_float4(ch_lo, cl_lo, ch_hi, cl_hi);
-    if (lane == 0) part[s][warp] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
+      carries[(s * kConsumerWarps + cw) * 32 + lane] = make_float4(ch_lo, cl_lo, ch_hi, cl_hi);
+    if (lane == 0) part[s][cw] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
     __syncwarp();
     if (lane == 0) mbar_arrive(p1done0 + 8 * s);
+    LB_ADD(5, threadIdx.x == 0);
     return true;
   };
 
   // pass 2 of local tile k: the scan proper, seeded with everything before the slice
   auto pass2 = [&](uint32_t k) -> bool {
     const uint32_t s = k % NS, ph = (k / NS) & 1u;
-    if (!mbar_wait_or_stop(resolved0 + 8 * s, ph, abort_flag, nullptr, 0)) return false;
+    // the tile landed long ago (pass 1 has read it); this wait returns at once and makes the
+    // copy's bytes visible to this warp as well
+    {
+      LB_T0();
+      if (!mbar_wait_or_stop(full0 + 8 * s, ph, abort_flag, end_index, k)) return false;
+      if (!mbar_wait_or_stop(resolved0 + 8 * s, ph, abort_flag, end_index, k)) return false;
+      LB_ADD(3, threadIdx.x == kPass2Warp0 * 32);
+    }
+    LB_T0();
     const unsigned long long tile = stage_tile[s];
     const SliceView v = slice_view(s, tile);
     double carry = tile_excl[s];
-    for (int w = 0; w < warp; ++w) carry += (double)part[s][w].x + (double)part[s][w].y;
+    for (int w = 0; w < cw; ++w) carry += (double)part[s][w].x + (double)part[s][w].y;
     const float xh = (float)carry;
     const float xl = (float)(carry - (double)xh);
     if (v.valid_bytes > 0) {
       float ch_lo, cl_lo, ch_hi, cl_hi;
       if constexpr (kSaveCarries) {
-        const float4 c = carries[(s * kConsumerWarps + warp) * 32 + lane];
+        const float4 c = carries[(s * kConsumerWarps + cw) * 32 + lane];
         ch_lo = c.x, cl_lo = c.y, ch_hi = c.z, cl_hi = c.w;
       } else {  // no room to keep them: redo the row totals
         Acc tot_h = zero, tot_l = zero;
@@ -345,21 +395,14 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    LB_ADD(6, threadIdx.x == kPass2Warp0 * 32);
     return true;
   };
 
-  uint32_t p1_next = 0;
-  bool more = true;
-  while (more && p1_next < (uint32_t)kLookahead) {
-    more = pass1(p1_next);
-    if (more) ++p1_next;
-  }
-  for (uint32_t k = 0; k < p1_next; ++k) {
-    if (!pass2(k)) break;
-    if (more) {
-      more = pass1(p1_next);
-      if (more) ++p1_next;
-    }
+  if (warp < kPass2Warp0) {
+    for (uint32_t i = 0; pass1(i); ++i) {}
+  } else {
+    for (uint32_t k = 0; pass2(k); ++k) {}
   }
 }
 
