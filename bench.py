@@ -414,6 +414,42 @@ def cub_leg(torch, tcu, args):
     return out
 
 
+def ablation_leg(torch, tcu, args):
+    """In-run ablation: the same TMA pipeline with CUDA-core adds and warp shuffles in place of
+    the tensor-core contraction (TCU_ALGO_SHUFFLE), on the sweep and on the segmented scans."""
+    n = 1 << min(args.log2_elems, 28)
+    xs = [tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024 + i, 0) for i in range(2)]
+    k = [0]
+    out = {"unit": "Gelem/s", "reduce": {}, "scan": {}}
+    for algo in ("mma", "shuffle"):
+        red, total_ms = {}, 0.0
+        for s in SWEEP:
+            o = torch.empty(n // s, dtype=torch.float32, device="cuda")
+
+            def call():
+                k[0] += 1
+                tcu.segmented_reduce(xs[k[0] % 2], s, out=o, algo=algo)
+            ms, _ = time_op(torch, call, 10, 3)
+            total_ms += ms
+            red[str(s)] = round(n / ms / 1e6, 1)
+        red["sweep"] = round(len(SWEEP) * n / total_ms / 1e6, 1)
+        out["reduce"][algo] = red
+        sc = {}
+        for s, dt in [(16, torch.float16), (256, torch.float16), (4096, torch.float32)]:
+            o = torch.empty(n, dtype=dt, device="cuda")
+
+            def call():
+                k[0] += 1
+                tcu.segmented_scan(xs[k[0] % 2], s, out=o, algo=algo)
+            ms, _ = time_op(torch, call, 10, 3)
+            sc[f"{s}_{'f32' if dt == torch.float32 else 'f16'}"] = round(n / ms / 1e6, 1)
+            del o
+        out["scan"][algo] = sc
+    out["note"] = ("direct launches, CUDA events around 10 back-to-back calls; the shuffle variant "
+                   "does not split inputs into exact parts (plain fp32 rounding)")
+    return out
+
+
 def run_e2e(torch, tcu, dist, args, rank, world):
     """Same sweep through the host-buffer entry point: pinned host input, results read back."""
     import numpy as np
@@ -635,6 +671,7 @@ def _main(args, json_fd):
             cb = cub_leg(torch, tcu, args)
             if cb is not None:
                 result["cub_on_this_gpu"] = cb
+            result["ablation_tensor_core_vs_shuffle"] = ablation_leg(torch, tcu, args)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

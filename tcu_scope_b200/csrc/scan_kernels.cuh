@@ -87,18 +87,46 @@ struct ScanGeom {
   }
 };
 
+// Where lane (g,t) finds its 8 bytes of MMA row g at step j (row g+8 is
+// kHiOffset further).  kSwz: the tile was written by a swizzled tensor-map copy
+// (slices start on 4 KiB boundaries of a 1 KiB-aligned tile, so the swizzle
+// only depends on the offset inside the slice).  The swizzled offset of
+// 256g + 32j + 8t has the closed form
+//   256g + 128(j>>2) + 8(t&1) + 16((t>>1) ^ (j>>2)) + 32((j&3) ^ (g&3)),
+// i.e. one of two lane-constant bases plus one of four lane-constant terms:
+// one add per load instead of a shift-mask-xor sequence.
+template <class Geom, bool kSwz>
+struct SliceAddr {
+  const uint8_t* base[2];
+  int term[4];
+  __device__ __forceinline__ SliceAddr(const uint8_t* slice, int g, int t) {
+    if constexpr (kSwz) {
+      base[0] = slice + 256 * g + 8 * (t & 1) + 16 * (t >> 1);
+      base[1] = slice + 256 * g + 128 + 8 * (t & 1) + 16 * ((t >> 1) ^ 1);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) term[c] = 32 * (c ^ (g & 3));
+    } else {
+      base[0] = base[1] = slice + Geom::lo(g, t, 0);
+      term[0] = term[1] = term[2] = term[3] = 0;
+    }
+  }
+  __device__ __forceinline__ const uint8_t* lo(int j) const {
+    if constexpr (kSwz)
+      return base[j >> 2] + term[j & 3];
+    else
+      return base[0] + (Geom::lo(0, 0, j) - Geom::lo(0, 0, 0));  // compile-time offset
+  }
+};
+
 // Load the 2 x 8 bytes lane (g,t) owns at step j and split them into exact
 // hi / lo A operands: [0] row g k 2t,2t+1  [1] row g+8 k 2t,2t+1
 //                     [2] row g k 2t+8,+9  [3] row g+8 k 2t+8,+9.
-// kSwz: the tile was written by a swizzled tensor-map copy (slices start on
-// 4 KiB boundaries of a 1 KiB-aligned tile, so the swizzle only depends on the
-// offset inside the slice).
-template <class Geom, bool kSwz = false>
-__device__ __forceinline__ void load_split(const uint8_t* slice, int g, int t, int j,
+template <class Geom, bool kSwz>
+__device__ __forceinline__ void load_split(const SliceAddr<Geom, kSwz>& addr, int j,
                                            uint32_t (&ah)[4], uint32_t (&al)[4]) {
-  const int off_lo = Geom::lo(g, t, j), off_hi = off_lo + Geom::kHiOffset;
-  const uint2 lo = lds64(slice + (kSwz ? swizzle128(off_lo) : off_lo));
-  const uint2 hi = lds64(slice + (kSwz ? swizzle128(off_hi) : off_hi));
+  const uint8_t* p = addr.lo(j);
+  const uint2 lo = lds64(p);
+  const uint2 hi = lds64(p + Geom::kHiOffset);
   split_hi_lo(lo.x, ah[0], al[0]);
   split_hi_lo(hi.x, ah[1], al[1]);
   split_hi_lo(lo.y, ah[2], al[2]);
@@ -151,13 +179,15 @@ __device__ __forceinline__ void row_carries(const Acc& tot_h, const Acc& tot_l, 
 
 // One step of one slice: 16 rows x 16 elements.  D = A.U + carry for the hi
 // and the lo parts (4 MMAs), the carry for the next step (2 more, only when a
-// segment continues), then out = hi + lo (+ the carry from earlier slices).
-template <int SC, bool OUT32, bool kExtraCarry>
+// segment continues), then out = hi + lo.  The carry from earlier slices of the
+// segment is not added here per output: the caller adds it once to the row
+// carries, and it rides through the accumulator operand with them.
+template <int SC, bool OUT32>
 __device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const uint32_t (&al)[4],
                                           const ScanOperands& ops, float& ch_lo, float& cl_lo,
-                                          float& ch_hi, float& cl_hi, float xh, float xl,
-                                          void* out, unsigned long long elem_base,
-                                          int valid_elems, int g, int t) {
+                                          float& ch_hi, float& cl_hi, void* out,
+                                          unsigned long long elem_base, int valid_elems, int g,
+                                          int t) {
   using Geom = ScanGeom<SC>;
   // a new segment starts inside the row at this step: drop the carry
   if (SC == 4 || (SC == 5 && (j & 1) == 0) || (SC == 6 && (j & 3) == 0))
@@ -177,21 +207,12 @@ __device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const 
     cl_hi = nl.d2;
   }
   const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
-  if constexpr (kExtraCarry) {
-    if (e_lo < valid_elems)
-      store4<OUT32>(out, elem_base + e_lo, (ha.d0 + xh) + (la.d0 + xl), (ha.d1 + xh) + (la.d1 + xl),
-                    (hb.d0 + xh) + (lb.d0 + xl), (hb.d1 + xh) + (lb.d1 + xl));
-    if (e_hi < valid_elems)
-      store4<OUT32>(out, elem_base + e_hi, (ha.d2 + xh) + (la.d2 + xl), (ha.d3 + xh) + (la.d3 + xl),
-                    (hb.d2 + xh) + (lb.d2 + xl), (hb.d3 + xh) + (lb.d3 + xl));
-  } else {
-    if (e_lo < valid_elems)
-      store4<OUT32>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
-                    hb.d1 + lb.d1);
-    if (e_hi < valid_elems)
-      store4<OUT32>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
-                    hb.d3 + lb.d3);
-  }
+  if (e_lo < valid_elems)
+    store4<OUT32>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
+                  hb.d1 + lb.d1);
+  if (e_hi < valid_elems)
+    store4<OUT32>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
+                  hb.d3 + lb.d3);
 }
 
 // Variant of scan_step for rows that are chained over all eight steps, with
@@ -206,8 +227,7 @@ template <int SC, bool OUT32>
 __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah)[4],
                                                       const uint32_t (&al)[4],
                                                       const ScanOperands& ops, RowCarry& c,
-                                                      float xh, float xl, void* out,
-                                                      unsigned long long elem_base,
+                                                      void* out, unsigned long long elem_base,
                                                       int valid_elems, int g, int t) {
   using Geom = ScanGeom<SC>;
   const Acc zero{0.f, 0.f, 0.f, 0.f};
@@ -225,11 +245,11 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
   }
   const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
   if (e_lo < valid_elems)
-    store4<OUT32>(out, elem_base + e_lo, (ha.d0 + xh) + (la.d0 + xl), (ha.d1 + xh) + (la.d1 + xl),
-                  (hb.d0 + xh) + (lb.d0 + xl), (hb.d1 + xh) + (lb.d1 + xl));
+    store4<OUT32>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
+                  hb.d1 + lb.d1);
   if (e_hi < valid_elems)
-    store4<OUT32>(out, elem_base + e_hi, (ha.d2 + xh) + (la.d2 + xl), (ha.d3 + xh) + (la.d3 + xl),
-                  (hb.d2 + xh) + (lb.d2 + xl), (hb.d3 + xh) + (lb.d3 + xl));
+    store4<OUT32>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
+                  hb.d3 + lb.d3);
 }
 
 // Segment classes as for the reduction: 4..11 = 2^class elements (inside one
@@ -308,13 +328,14 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
     if (active && valid_bytes < kSliceBytes) zero_slice_tail(slice, valid_bytes, lane);
 
     // ---- load + split the whole slice; row totals for classes that chain rows
+    const SliceAddr<Geom, false> addr(slice, g, t);
     constexpr int kKeep = kScanCache ? 8 : 1;
     uint32_t ah[kKeep][4], al[kKeep][4];
     Acc tot_h = zero, tot_l = zero;
     if (active && (kScanCache || SC >= 8)) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        load_split<Geom>(slice, g, t, j, ah[kScanCache ? j : 0], al[kScanCache ? j : 0]);
+        load_split(addr, j, ah[kScanCache ? j : 0], al[kScanCache ? j : 0]);
         if constexpr (SC >= 8) {
           tot_h = mma_ones(ah[kScanCache ? j : 0], tot_h);
           tot_l = mma_ones(al[kScanCache ? j : 0], tot_l);
@@ -344,6 +365,11 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
           xh += pr.x;
           xl += pr.y;
         }
+        // everything before this slice in its segment rides along with the row carries
+        ch_lo += xh;
+        ch_hi += xh;
+        cl_lo += xl;
+        cl_hi += xl;
       }
     }
     if (active) {
@@ -351,10 +377,9 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
       const int valid_elems = valid_bytes / 2;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        if constexpr (!kScanCache) load_split<Geom>(slice, g, t, j, ah[0], al[0]);  // second read
-        scan_step<SC, OUT32, (SC >= 12)>(j, ah[kScanCache ? j : 0], al[kScanCache ? j : 0], ops, ch_lo,
-                                         cl_lo, ch_hi, cl_hi, xh, xl, p.out, elem_base, valid_elems,
-                                         g, t);
+        if constexpr (!kScanCache) load_split(addr, j, ah[0], al[0]);  // second read
+        scan_step<SC, OUT32>(j, ah[kScanCache ? j : 0], al[kScanCache ? j : 0], ops, ch_lo, cl_lo,
+                             ch_hi, cl_hi, p.out, elem_base, valid_elems, g, t);
       }
     }
     if constexpr (!kScanCache) {

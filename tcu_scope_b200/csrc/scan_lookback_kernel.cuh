@@ -39,7 +39,13 @@ constexpr bool kSaveCarries         = TCU_LB_SAVE_CARRIES != 0;
 #define TCU_LOOKAHEAD 4
 #endif
 constexpr int kLookahead            = TCU_LOOKAHEAD;  // pass 1 runs this many tiles ahead of pass 2
-constexpr int kLookbackWarps        = 4;
+#ifndef TCU_LB_WARPS
+#define TCU_LB_WARPS 6
+#endif
+constexpr int kLookbackWarps        = TCU_LB_WARPS;
+// A look-back warp's first tile must be in the first pass over the ring: a
+// wait for a later phase on a fresh barrier would fall through.
+static_assert(kLookbackWarps <= kLookbackStages, "at most one look-back warp per ring stage");
 constexpr int kLookbackCtasPerSm    = 1;
 // Warp roles: [0,8) pass-1 warps, [8,16) pass-2 warps, 16 producer, 17.. look-back.
 // Pass 1 and pass 2 of different tiles run at the same time on different warps:
@@ -93,15 +99,23 @@ __device__ __forceinline__ unsigned long long status_load(const unsigned long lo
 // index `first` (found_inclusive = false: the sum covers [first, last] only).
 // Each poll reads one word per lane (256 bytes per warp); words already summed
 // are never read again, and a poll that makes no progress backs off.
+//
+// `prefetched` (with use_prefetched) is the word this lane would read in the
+// first window, loaded earlier by the caller -- the block-level window is
+// fetched in the same round trip as the tile-level one.
 __device__ __forceinline__ double look_back(const unsigned long long* status, long long last,
-                                            long long first, int lane, bool& found_inclusive) {
+                                            long long first, int lane, bool& found_inclusive,
+                                            bool use_prefetched = false,
+                                            unsigned long long prefetched = 0ull) {
   double sum     = 0.0;
   uint32_t polls = 0;
   found_inclusive = false;
   while (last >= first) {
     const long long idx = last - lane;
     const bool valid    = idx >= first;
-    const unsigned long long w = valid ? status_load(status + idx) : 0ull;
+    const unsigned long long w =
+        use_prefetched ? prefetched : (valid ? status_load(status + idx) : 0ull);
+    use_prefetched = false;
     const unsigned state = static_cast<unsigned>(w & 3ull);
     const unsigned not_ready = __ballot_sync(0xffffffffu, valid && state == 0u);
     const unsigned stops     = __ballot_sync(0xffffffffu, !valid || state == kStateInclusive);
@@ -256,6 +270,11 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
         if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
       } else {
         if (lane == 0) status_store(p.tile_status + tile, agg, kStateAggregate);
+        // first window of the block-level walk, in flight together with the tile-level one
+        const long long blk_last = (long long)(blk_base + blk) - 1;
+        const long long blk_idx  = blk_last - lane;
+        const unsigned long long blk_word =
+            blk_idx >= (long long)blk_base ? status_load(p.block_status + blk_idx) : 0ull;
         bool complete = false;
         const double in_block = look_back(p.tile_status, (long long)tile - 1,
                                           (long long)blk_first, lane, complete);
@@ -264,8 +283,8 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
           if (closes_block && lane == 0)
             status_store(p.block_status + blk_base + blk, in_block + agg, kStateAggregate);
           bool dummy;
-          before_block = look_back(p.block_status, (long long)(blk_base + blk) - 1,
-                                   (long long)blk_base, lane, dummy);
+          before_block = look_back(p.block_status, blk_last, (long long)blk_base, lane, dummy,
+                                   /*use_prefetched=*/true, blk_word);
         }
         excl = before_block + in_block;
         if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
@@ -328,10 +347,11 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       if (active && v.valid_bytes < kSliceBytes) zero_slice_tail(v.slice, v.valid_bytes, lane);
     Acc tot_h = zero, tot_l = zero;
     if (active) {
+      const SliceAddr<Geom, kSwz> addr(v.slice, g, t);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
-        load_split<Geom, kSwz>(v.slice, g, t, j, ah, al);
+        load_split(addr, j, ah, al);
         tot_h = mma_ones(ah, tot_h);
         tot_l = mma_ones(al, tot_l);
       }
@@ -363,10 +383,15 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     const SliceView v = slice_view(s, tile);
     double carry = tile_excl[s];
     for (int w = 0; w < cw; ++w) carry += (double)part[s][w].x + (double)part[s][w].y;
-    const float xh = (float)carry;
+    // Everything before this slice, as two floats that ride through the MMAs'
+    // accumulator operand with the row carries: xh a multiple of 2^-13 (what the
+    // hi parts are made of, so sums below 2^11 stay exact), xl the small rest.
+    const double carry_hi = rint(carry * 8192.0) * (1.0 / 8192.0);
+    const float xh = (float)carry_hi;
     const float xl = (float)(carry - (double)xh);
     if (v.valid_bytes > 0) {
       float ch_lo, cl_lo, ch_hi, cl_hi;
+      const SliceAddr<Geom, kSwz> addr(v.slice, g, t);
       if constexpr (kSaveCarries) {
         const float4 c = carries[(s * kConsumerWarps + cw) * 32 + lane];
         ch_lo = c.x, cl_lo = c.y, ch_hi = c.z, cl_hi = c.w;
@@ -375,22 +400,21 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint32_t ah[4], al[4];
-          load_split<Geom, kSwz>(v.slice, g, t, j, ah, al);
+          load_split(addr, j, ah, al);
           tot_h = mma_ones(ah, tot_h);
           tot_l = mma_ones(al, tot_l);
         }
         float slice_h, slice_l;
         row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
       }
-      RowCarry rc{ch_lo, cl_lo, ch_hi, cl_hi};
+      RowCarry rc{ch_lo + xh, cl_lo + xl, ch_hi + xh, cl_hi + xl};
       const unsigned long long elem_base = v.slice_off / 2;
       const int valid_elems = v.valid_bytes / 2;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
-        load_split<Geom, kSwz>(v.slice, g, t, j, ah, al);
-        scan_step_independent<SC, OUT32>(j, ah, al, ops, rc, xh, xl, p.out, elem_base, valid_elems,
-                                         g, t);
+        load_split(addr, j, ah, al);
+        scan_step_independent<SC, OUT32>(j, ah, al, ops, rc, p.out, elem_base, valid_elems, g, t);
       }
     }
     __syncwarp();
