@@ -88,13 +88,30 @@ cudaError_t ensure_smem(K kernel, bool* configured, int bytes) {
   return cudaSuccess;
 }
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may be
+// scheduled while its predecessor in the stream drains (see pdl_prologue()).
+template <typename Params>
+cudaError_t launch_pdl(void (*kernel)(Params), const Params& p, int grid, int threads,
+                       size_t smem, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim          = dim3(grid);
+  cfg.blockDim         = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream           = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs    = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 template <int SC>
 cudaError_t launch_reduce(const ReduceParams& p, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
   cudaError_t e = ensure_smem(seg_reduce_kernel<SC, true>, configured, kDynSmemBytes);
   if (e != cudaSuccess) return e;
-  seg_reduce_kernel<SC, true><<<grid, kThreads, kDynSmemBytes, st>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(seg_reduce_kernel<SC, true>, p, grid, kThreads, kDynSmemBytes, st);
 }
 
 template <int SC, bool OUT32>
@@ -102,9 +119,8 @@ cudaError_t launch_scan(const ScanParams& p, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
   cudaError_t e = ensure_smem(seg_scan_kernel<SC, OUT32>, configured, scan_dyn_smem_bytes(SC));
   if (e != cudaSuccess) return e;
-  seg_scan_kernel<SC, OUT32>
-      <<<grid * scan_ctas_per_sm(SC), kThreads, scan_dyn_smem_bytes(SC), st>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(seg_scan_kernel<SC, OUT32>, p, grid * scan_ctas_per_sm(SC), kThreads,
+                    scan_dyn_smem_bytes(SC), st);
 }
 
 // cuTensorMapEncodeTiled, looked up once through the runtime (no link against libcuda).

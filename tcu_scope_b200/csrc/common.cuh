@@ -111,6 +111,16 @@ constexpr int kTileRows = kTileElems / kSwizzleRowElems;  // 256 rows per tile (
 // Byte offset inside a 1024-byte-aligned tile after the 128-byte swizzle.
 __device__ __forceinline__ int swizzle128(int off) { return off ^ (((off >> 7) & 7) << 4); }
 
+// Programmatic dependent launch.  Every kernel of the library lets the next
+// kernel in the stream be scheduled early (its CTAs start as SMs drain, and do
+// their barrier set-up) and itself touches global memory only after everything
+// launched before it has completed and is visible.  Both are no-ops for
+// launches made without the programmatic-serialization attribute.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // Named barrier over the consumer warps only (the producer warp never joins).
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");

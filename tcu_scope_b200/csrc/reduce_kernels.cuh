@@ -254,6 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_prologue();  // nothing above touched global memory
 
   const unsigned long long total_bytes = p.num_elems * 2ull;
   const unsigned long long num_tiles   = (total_bytes + kTileBytes - 1) / kTileBytes;

@@ -288,6 +288,7 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_prologue();  // nothing above touched global memory
 
   const unsigned long long total_bytes = p.num_elems * 2ull;
   const unsigned long long num_tiles   = (total_bytes + kTileBytes - 1) / kTileBytes;
