@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kStages];
   __shared__ float2 part[2][kConsumerWarps];  // slice totals of the tile in flight
-  __shared__ double warp_sum[kConsumerWarps]; // full reduction: per-warp running sums
+  __shared__ double warp_sum[2][kConsumerWarps];  // long class: per-warp running sums of a segment
   __shared__ int s_is_last;
 
   // 128-byte aligned ring, whatever offset the dynamic segment starts at
@@ -306,6 +306,31 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
       p.bound_seg[2 * blockIdx.x] = -1;
       p.bound_seg[2 * blockIdx.x + 1] = -1;
     }
+    // Collective over the consumer warps: add up their running sums of segment run_seg and
+    // write the result where it belongs -- the output if this CTA saw the whole segment, else
+    // one of the CTA's two boundary records (head: began in an earlier CTA; tail: goes on).
+    uint32_t flushes = 0;
+    auto flush_segment = [&](bool segment_complete) {
+      const uint32_t buf = flushes++ & 1u;
+      if (lane == 0) warp_sum[buf][warp] = run_val;
+      consumer_sync();
+      if (warp == 0 && lane == 0) {
+        double total = 0.0;
+        for (int w = 0; w < kConsumerWarps; ++w) total += warp_sum[buf][w];
+        if (run_is_head) {
+          p.bound_val[2 * blockIdx.x] = total;
+          p.bound_seg[2 * blockIdx.x] = run_seg;
+        } else if (segment_complete) {
+          store_seg(p.out, out_f32, run_seg, (float)total);
+          if (p.out_f64) p.out_f64[run_seg] = total;
+        } else {
+          p.bound_val[2 * blockIdx.x + 1] = total;
+          p.bound_seg[2 * blockIdx.x + 1] = run_seg;
+        }
+        // no fence here: this is thread 0, which fences once before it takes the completion
+        // ticket below (a fence per segment costs more than the segment's tiles)
+      }
+    };
 
     uint32_t i = 0;
     for (unsigned long long tile = tile_begin; tile < tile_end; tile += tile_step, ++i) {
@@ -330,12 +355,24 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
 
-      if (single) {
-        // one segment: no per-tile meeting of the warps, each keeps its own running sum
+      if constexpr (SC == kClassLong) {
+        // Long segments: every warp keeps its own running sum of the current segment and the
+        // warps only meet when the segment changes (all warps track the segment of a tile the
+        // same way, so the meeting is collective).  One segment: they meet once, at the end.
+        if (!single) {
+          if (run_seg >= 0 && ++tile_in_seg == p.tiles_per_segment) {  // no 64-bit division per tile
+            tile_in_seg = 0;
+            ++next_seg;
+          }
+          if (next_seg != run_seg) {
+            if (run_seg >= 0) flush_segment(/*segment_complete=*/true);
+            run_seg     = next_seg;
+            run_val     = 0.0;
+            run_is_head = tile_in_seg != 0;  // began in an earlier CTA
+          }
+        }
         run_val += (double)tot.x + (double)tot.y;
-        continue;
-      }
-      if constexpr (SC >= 12) {
+      } else if constexpr (SC >= 12) {
         // combine the slice totals of this tile across warps
         if (lane == 0) part[i & 1][warp] = tot;
         consumer_sync();
@@ -345,65 +382,20 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
           constexpr int kWarpsPerSeg = SC == 12 ? 2 : (SC == 13 ? 4 : 8);
 #pragma unroll
           for (int m = 1; m < kWarpsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-          if constexpr (SC != kClassLong) {
-            const unsigned long long seg = tile * (8 / kWarpsPerSeg) + lane / kWarpsPerSeg;
-            if (lane < 8 && (lane % kWarpsPerSeg) == 0 && seg < p.num_segments && !dead)
-              store_seg(p.out, out_f32, seg, (float)v);
-          } else if (lane == 0) {
-            // v = exact total of this tile; extend or flush the running segment
-            // segment of this tile without a 64-bit division per tile: tiles of a
-            // CTA are consecutive here (or all in segment 0)
-            if (!single && run_seg >= 0 && ++tile_in_seg == p.tiles_per_segment) {
-              tile_in_seg = 0;
-              ++next_seg;
-            }
-            const long long seg = next_seg;
-            if (seg != run_seg) {
-              if (run_seg >= 0) {
-                if (run_is_head) {
-                  p.bound_val[2 * blockIdx.x] = run_val;
-                  p.bound_seg[2 * blockIdx.x] = run_seg;
-                } else {
-                  store_seg(p.out, out_f32, run_seg, (float)run_val);
-                  if (p.out_f64) p.out_f64[run_seg] = run_val;
-                }
-              }
-              run_seg     = seg;
-              run_val     = 0.0;
-              // began in an earlier CTA (with one segment every CTA holds a piece of it)
-              run_is_head = single || tile_in_seg != 0;
-            }
-            run_val += v;
-          }
+          const unsigned long long seg = tile * (8 / kWarpsPerSeg) + lane / kWarpsPerSeg;
+          if (lane < 8 && (lane % kWarpsPerSeg) == 0 && seg < p.num_segments && !dead)
+            store_seg(p.out, out_f32, seg, (float)v);
         }
       }
     }
 
     if constexpr (SC == kClassLong) {
-      if (single) {  // the warps' running sums meet once, in warp order
-        if (lane == 0) warp_sum[warp] = run_val;
-        consumer_sync();
-        if (warp == 0 && lane == 0) {
-          double total = 0.0;
-          for (int w = 0; w < kConsumerWarps; ++w) total += warp_sum[w];
-          p.bound_val[2 * blockIdx.x] = total;
-          p.bound_seg[2 * blockIdx.x] = 0;
-          __threadfence();
-        }
-      } else if (warp == 0 && lane == 0 && run_seg >= 0) {
-        const bool ends_here = (tile_end % p.tiles_per_segment) == 0;  // segment complete
-        if (run_is_head) {
-          p.bound_val[2 * blockIdx.x] = run_val;
-          p.bound_seg[2 * blockIdx.x] = run_seg;
-        } else if (ends_here) {
-          store_seg(p.out, out_f32, run_seg, (float)run_val);
-          if (p.out_f64) p.out_f64[run_seg] = run_val;
-        } else {
-          p.bound_val[2 * blockIdx.x + 1] = run_val;
-          p.bound_seg[2 * blockIdx.x + 1] = run_seg;
-        }
-        __threadfence();
+      if (single) {
+        run_seg     = 0;
+        run_is_head = true;  // every CTA holds a piece of the one segment
       }
+      if (run_seg >= 0 || single)
+        flush_segment(/*segment_complete=*/!single && (tile_end % p.tiles_per_segment) == 0);
     }
   }
 
