@@ -113,6 +113,20 @@ int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_el
                       void* d_workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Exclusive variants: out[i] = sum of the elements of the segment BEFORE i (0 for
+ * the first).  The reference has inclusive scans only (U has ones on its
+ * diagonal, src/prefixsum/kernel.cuh:60); callers that turn counts into offsets
+ * need this form, and on the tensor core it is the same product with the
+ * diagonal of U removed.  Arguments as for the inclusive entry points; always
+ * the tensor-core algorithm.
+ */
+int tcu_segmented_exclusive_scan_f16(const void* d_in, void* d_out, int out_type,
+                                     size_t num_segments, size_t segment_size, void* d_workspace,
+                                     size_t workspace_bytes, void* stream);
+int tcu_full_exclusive_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                                void* d_workspace, size_t workspace_bytes, void* stream);
+
+/*
  * tcu_full_scan_f16 for callers that must not allocate device memory.  It has
  * no counterpart in the reference, whose drivers cudaMalloc whatever they need.
  *

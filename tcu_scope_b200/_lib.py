@@ -25,6 +25,10 @@ SIGNATURES = {
                                     c_size_t, c_void_p]),
     "tcu_full_scan_f16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int, c_int,
                                   c_void_p, c_size_t, c_void_p]),
+    "tcu_segmented_exclusive_scan_f16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t,
+                                                 c_void_p, c_size_t, c_void_p]),
+    "tcu_full_exclusive_scan_f16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p,
+                                            c_size_t, c_void_p]),
     "tcu_full_scan_f16_static": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int,
                                          c_int, c_void_p]),
     "tcu_workspace_bytes": (c_size_t, [c_int, c_size_t, c_size_t]),

@@ -263,7 +263,7 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
 
 int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
               size_t segment_size, int sc, const double* shard_totals, int shard_index, int algo,
-              void* ws, size_t ws_bytes, cudaStream_t st) {
+              void* ws, size_t ws_bytes, cudaStream_t st, bool exclusive = false) {
   if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
   if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE)
     return TCU_ERR_UNSUPPORTED;
@@ -280,6 +280,8 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   p.out        = d_out;
   p.num_elems  = n;
   p.out_is_f32 = out_type == TCU_OUT_F32;
+  p.exclusive  = exclusive ? 1 : 0;
+  if (exclusive && algo == TCU_ALGO_SHUFFLE) return TCU_ERR_UNSUPPORTED;  // ablation: inclusive only
   const size_t tiles = (n + kTileElems - 1) / kTileElems;
   const int grid     = tiles < size_t(sms) ? int(tiles) : sms;
   const bool f32     = out_type == TCU_OUT_F32;
@@ -351,6 +353,22 @@ int tcu_segmented_scan_f16(const void* d_in, void* d_out, int out_type, size_t n
   if (sc < 0) return TCU_ERR_UNSUPPORTED;
   return scan_impl(d_in, d_out, out_type, num_segments, segment_size, sc, nullptr, 0, algo,
                    d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int tcu_segmented_exclusive_scan_f16(const void* d_in, void* d_out, int out_type,
+                                     size_t num_segments, size_t segment_size, void* d_workspace,
+                                     size_t workspace_bytes, void* stream) {
+  const int sc = segment_class(segment_size);
+  if (sc < 0) return TCU_ERR_UNSUPPORTED;
+  return scan_impl(d_in, d_out, out_type, num_segments, segment_size, sc, nullptr, 0, TCU_ALGO_MMA,
+                   d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream), true);
+}
+
+int tcu_full_exclusive_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                                void* d_workspace, size_t workspace_bytes, void* stream) {
+  if (num_elements % 16 != 0) return TCU_ERR_INVALID_ARG;
+  return scan_impl(d_in, d_out, out_type, 1, num_elements, kClassLong, nullptr, 0, TCU_ALGO_MMA,
+                   d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream), true);
 }
 
 // The full operations are the long class with a single segment covering every

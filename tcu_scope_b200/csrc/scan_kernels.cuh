@@ -36,6 +36,7 @@ struct ScanParams {
   unsigned int* ticket;                  // dynamic tile counter, zeroed by the host
   const double* shard_totals;            // optional: totals of all shards of a multi-GPU scan
   int shard_index;                       // this GPU's position in shard_totals
+  int exclusive;                         // 1: out[i] excludes in[i] (strictly triangular operand)
 };
 
 // B operands for "A times U" with the k order that the 8-byte row loads give:
@@ -47,9 +48,11 @@ struct ScanOperands {
   uint32_t ua0, ua1, ub0, ub1;
 };
 
-__device__ __forceinline__ ScanOperands make_scan_operands(int lane) {
+// exclusive: position p contributes to output q only if p < q, i.e. U without
+// its diagonal; row totals and carries do not change.
+__device__ __forceinline__ ScanOperands make_scan_operands(int lane, bool exclusive) {
   const int g = lane >> 2, t = lane & 3;
-  const int qa = 4 * (g >> 1) + (g & 1), qb = qa + 2;
+  const int qa = 4 * (g >> 1) + (g & 1) - (exclusive ? 1 : 0), qb = qa + 2;
   auto pack = [](bool e0, bool e1) -> uint32_t {
     return (e0 ? 0x3C00u : 0u) | (e1 ? 0x3C000000u : 0u);
   };
@@ -312,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
   // ------------------------------------------------------------- consumers
   using Geom = ScanGeom<SC>;
   const int g = lane >> 2, t = lane & 3;
-  const ScanOperands ops = make_scan_operands(lane);
+  const ScanOperands ops = make_scan_operands(lane, p.exclusive != 0);
   const Acc zero{0.f, 0.f, 0.f, 0.f};
   bool dead = false;
 

@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   using Geom = ScanGeom<SC>;
   const int cw = warp & (kConsumerWarps - 1);  // the slice this warp owns, in either pass
   const int g = lane >> 2, t = lane & 3;
-  const ScanOperands ops = make_scan_operands(lane);
+  const ScanOperands ops = make_scan_operands(lane, p.exclusive != 0);
   const Acc zero{0.f, 0.f, 0.f, 0.f};
 
   struct SliceView {

@@ -91,8 +91,9 @@ def segmented_reduce(x: torch.Tensor, segment_size: int, out_dtype=torch.float32
 
 
 def segmented_scan(x: torch.Tensor, segment_size: int, out_dtype=torch.float16, algo="auto",
-                   out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
-    """Inclusive prefix sum inside every segment of segment_size elements."""
+                   out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                   exclusive: bool = False):
+    """Prefix sum inside every segment of segment_size elements (inclusive unless ``exclusive``)."""
     _require_input(x)
     n = x.numel()
     if segment_size <= 0 or n % segment_size:
@@ -100,6 +101,11 @@ def segmented_scan(x: torch.Tensor, segment_size: int, out_dtype=torch.float16, 
     if out is None:
         out = torch.empty(n, dtype=out_dtype, device=x.device)
     ws, ws_ptr, ws_bytes = _workspace(OP_SEGMENTED_SCAN, n, segment_size, x.device, workspace)
+    if exclusive:
+        _check(_lib.load().tcu_segmented_exclusive_scan_f16(
+            x.data_ptr(), out.data_ptr(), _out_code(out.dtype), n // segment_size, segment_size,
+            ws_ptr, ws_bytes, _stream()), "tcu_segmented_exclusive_scan_f16")
+        return out
     _check(_lib.load().tcu_segmented_scan_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype),
                                               n // segment_size, segment_size, ALGO[algo], ws_ptr,
                                               ws_bytes, _stream()), "tcu_segmented_scan_f16")
@@ -124,7 +130,8 @@ def full_reduce(x: torch.Tensor, algo="auto", workspace: torch.Tensor | None = N
 
 def full_scan(x: torch.Tensor, out_dtype=torch.float32, algo="auto",
               shard_totals: torch.Tensor | None = None, shard_index: int = 0,
-              out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+              out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+              exclusive: bool = False):
     """Inclusive prefix sum over the whole tensor (seeded by earlier shards' totals)."""
     _require_input(x)
     n = x.numel()
@@ -133,6 +140,13 @@ def full_scan(x: torch.Tensor, out_dtype=torch.float32, algo="auto",
     if shard_totals is not None and shard_totals.dtype != torch.float64:
         raise TypeError("shard_totals must be float64")
     ws, ws_ptr, ws_bytes = _workspace(OP_FULL_SCAN, n, n, x.device, workspace)
+    if exclusive:
+        if shard_totals is not None:
+            raise ValueError("the exclusive full scan has no multi-GPU seed")
+        _check(_lib.load().tcu_full_exclusive_scan_f16(x.data_ptr(), out.data_ptr(),
+                                                       _out_code(out.dtype), n, ws_ptr, ws_bytes,
+                                                       _stream()), "tcu_full_exclusive_scan_f16")
+        return out
     st_ptr = shard_totals.data_ptr() if shard_totals is not None else None
     _check(_lib.load().tcu_full_scan_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype), n,
                                          st_ptr, shard_index, ALGO[algo], ws_ptr, ws_bytes,

@@ -208,6 +208,24 @@ def test_scan_exact_on_integers(tcu):
                                   oracle.np_segmented_scan(bits(x), s))
 
 
+@pytest.mark.parametrize("s", [16, 64, 256, 4096, 16384, 65536])
+def test_exclusive_scan(tcu, s):
+    """out[i] = prefix before i: the inclusive oracle shifted by one inside each segment."""
+    n = max(3 * s, 5 * TILE + 2048) // s * s
+    x = device_input(tcu, n, 300 + s, 0)
+    incl = oracle.np_segmented_scan(bits(x), s).reshape(-1, s)
+    ref = np.concatenate([np.zeros((incl.shape[0], 1)), incl[:, :-1]], axis=1).reshape(-1)
+    buf, out = guarded(n, torch.float32)
+    tcu.segmented_scan(x, s, out=out, exclusive=True)
+    check_f32(out, ref, exact=True)
+    assert_guards(buf, n)
+    assert check_f16(tcu.segmented_scan(x, s, out_dtype=torch.float16, exclusive=True), ref) <= 1
+    if s == 65536:
+        y = device_input(tcu, n, 301, 0, "uniform_01")
+        full = oracle.np_segmented_scan(bits(y), n)
+        check_f32(tcu.full_scan(y, exclusive=True), np.concatenate([[0.0], full[:-1]]))
+
+
 # -------------------------------------------------------------- closed forms
 def test_closed_forms(tcu):
     ones = torch.ones(1 << 16, dtype=torch.float16, device="cuda")
