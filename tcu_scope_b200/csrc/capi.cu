@@ -16,6 +16,7 @@
 #include "scan_kernels.cuh"
 #include "scan_lookback_kernel.cuh"
 #include "shuffle_kernels.cuh"
+#include "tcgen05_reduce_kernel.cuh"
 
 namespace {
 
@@ -146,14 +147,15 @@ EncodeTiledFn encode_tiled_fn() {
 // 2-D view of the fp16 input for the swizzled tile loads: rows of 64 halves
 // (128 bytes), one box = one tile = 256 rows.  False if the view cannot be made
 // (element count not a multiple of 64, or no encoder): callers fall back to
-// linear copies.
-bool make_input_tensor_map(CUtensorMap* map, const void* d_in, size_t num_elems) {
+// linear copies.  box_rows: rows per copy (256 = one 32 KiB tile, 128 = one UMMA tile).
+bool make_input_tensor_map(CUtensorMap* map, const void* d_in, size_t num_elems,
+                           unsigned box_rows = kTileRows) {
   if (num_elems % kSwizzleRowElems != 0) return false;
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
   const cuuint64_t dims[2]    = {kSwizzleRowElems, num_elems / kSwizzleRowElems};
   const cuuint64_t strides[1] = {kSwizzleRowElems * 2};
-  const cuuint32_t box[2]     = {kSwizzleRowElems, kTileRows};
+  const cuuint32_t box[2]     = {kSwizzleRowElems, box_rows};
   const cuuint32_t estr[2]    = {1, 1};
   if (dims[1] >= (cuuint64_t(1) << 32)) return false;
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(d_in), dims, strides, box,
@@ -169,6 +171,16 @@ cudaError_t launch_scan_lookback(const ScanParams& p, const CUtensorMap& map, in
       ensure_smem(scan_lookback_kernel<OUT32, kSwz>, configured, kLookbackDynSmemBytes);
   if (e != cudaSuccess) return e;
   scan_lookback_kernel<OUT32, kSwz><<<grid, kLookbackThreads, kLookbackDynSmemBytes, st>>>(p, map);
+  return cudaGetLastError();
+}
+
+template <int LOG2S>
+cudaError_t launch_tcgen05_reduce(const ReduceParams& p, const CUtensorMap& map, int grid,
+                                  cudaStream_t st) {
+  static bool configured[kMaxDevices];
+  cudaError_t e = ensure_smem(tcgen05_reduce_kernel<LOG2S>, configured, kUmmaDynSmemBytes);
+  if (e != cudaSuccess) return e;
+  tcgen05_reduce_kernel<LOG2S><<<grid, kUmmaThreads, kUmmaDynSmemBytes, st>>>(p, map);
   return cudaGetLastError();
 }
 
@@ -207,10 +219,14 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
                 size_t num_segments, size_t segment_size, int sc, int algo, void* ws,
                 size_t ws_bytes, cudaStream_t st) {
   if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
-  if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE)
+  if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE &&
+      algo != TCU_ALGO_TCGEN05)
     return TCU_ERR_UNSUPPORTED;
   size_t n = 0;
   if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
+  // the tcgen05 variant covers 16/32/64-element segments of arrays it can view as 64-wide rows
+  if (algo == TCU_ALGO_TCGEN05 && (sc < 4 || sc > 6 || n % kSwizzleRowElems != 0))
+    return TCU_ERR_UNSUPPORTED;
   if (n == 0) return TCU_OK;
   // short classes store vectors of outputs, the long class single values
   const uintptr_t out_mask = sc == kClassLong ? 3u : 15u;
@@ -231,6 +247,17 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   int grid           = tiles < size_t(sms) ? int(tiles) : sms;
 
   cudaError_t e = cudaSuccess;
+  if (algo == TCU_ALGO_TCGEN05) {
+    CUtensorMap map;
+    std::memset(&map, 0, sizeof(map));
+    if (!make_input_tensor_map(&map, d_in, n, kUmmaRows)) return TCU_ERR_CUDA;
+    const size_t utiles = (n + kUmmaTileElems - 1) / kUmmaTileElems;
+    const int ugrid     = utiles < size_t(sms) ? int(utiles) : sms;
+    e = sc == 4   ? launch_tcgen05_reduce<4>(p, map, ugrid, st)
+        : sc == 5 ? launch_tcgen05_reduce<5>(p, map, ugrid, st)
+                  : launch_tcgen05_reduce<6>(p, map, ugrid, st);
+    return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+  }
   if (sc == kClassLong) {
     if (!ws || ws_bytes < reduce_long_ws_bytes() || !aligned16(ws)) return TCU_ERR_WORKSPACE;
     if (grid > kMaxLongGrid) grid = kMaxLongGrid;

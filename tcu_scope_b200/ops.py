@@ -15,7 +15,7 @@ import torch
 from . import _lib
 
 OK = 0
-ALGO = {"auto": 0, "mma": 1, "shuffle": 2}
+ALGO = {"auto": 0, "mma": 1, "shuffle": 2, "tcgen05": 3}
 OUT_F16, OUT_F32 = 0, 1
 OP_SEGMENTED_REDUCE, OP_SEGMENTED_SCAN, OP_FULL_REDUCE, OP_FULL_SCAN = 0, 1, 2, 3
 DIST = {"uniform_pm1": 0, "uniform_01": 1, "small_int": 2, "const_0p001": 3}

@@ -1,0 +1,46 @@
+"""The tcgen05 / tensor-memory variant of the short-segment reduction (TCU_ALGO_TCGEN05)
+against the oracle and against the mma.sync path."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(t):
+    return t.cpu().view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("s", [16, 32, 64])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
+def test_tcgen05_reduce_matches_oracle(s, out_dtype):
+    import tcu_scope_b200 as tcu
+    # one row, a partial tile, whole tiles, many tiles per SM (ring and accumulators wrap)
+    for n in (64, 64 * 37, 8192, 8192 * 5 + 64 * 3, 1 << 20, (1 << 25) + 64 * 11):
+        x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 70 + s, 0)
+        buf = torch.full((n // s + 128,), -777.0, dtype=out_dtype, device="cuda")
+        out = buf[64:64 + n // s]
+        tcu.segmented_reduce(x, s, out=out, algo="tcgen05")
+        ref = oracle.c_segmented_reduce(bits(x), s)
+        if out_dtype == torch.float32:
+            bad, max_abs, _ = oracle.np_check_f32(out.cpu().numpy(), ref, 1e-3, 1e-5)
+            assert bad == 0, (n, max_abs)
+        else:
+            assert oracle.np_check_f16(bits(out), ref, 2)[0] == 0
+        guards = torch.cat([buf[:64], buf[64 + n // s:]]).float().cpu()
+        assert torch.all(guards == -777.0)
+        assert tcu.device_error() == 0
+    ints = tcu.fill(torch.empty(1 << 18, dtype=torch.float16, device="cuda"), 5, 0, "small_int")
+    assert torch.equal(tcu.segmented_reduce(ints, s, algo="tcgen05"), tcu.segmented_reduce(ints, s, algo="mma"))
+
+
+def test_tcgen05_rejects_what_it_does_not_cover():
+    import tcu_scope_b200 as tcu
+    x = tcu.fill(torch.empty(4096, dtype=torch.float16, device="cuda"), 1, 0)
+    with pytest.raises(tcu.TcuError) as e:
+        tcu.segmented_reduce(x, 256, algo="tcgen05")  # only 16/32/64-element segments
+    assert e.value.status == 2
+    with pytest.raises(tcu.TcuError):
+        tcu.segmented_reduce(x[:4096 - 16], 16, algo="tcgen05")  # element count not a multiple of 64
