@@ -419,7 +419,8 @@ def cub_leg(torch, tcu, args):
 
 def ablation_leg(torch, tcu, args):
     """In-run ablation: the same TMA pipeline with CUDA-core adds and warp shuffles in place of
-    the tensor-core contraction (TCU_ALGO_SHUFFLE), on the sweep and on the segmented scans."""
+    the tensor-core contraction (TCU_ALGO_SHUFFLE), on the sweep and on the segmented scans, and
+    the tcgen05 / tensor-memory form of the 16/32/64-element reductions (TCU_ALGO_TCGEN05)."""
     n = 1 << min(args.log2_elems, 28)
     xs = [tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024 + i, 0) for i in range(2)]
     k = [0]
@@ -448,8 +449,19 @@ def ablation_leg(torch, tcu, args):
             sc[f"{s}_{'f32' if dt == torch.float32 else 'f16'}"] = round(n / ms / 1e6, 1)
             del o
         out["scan"][algo] = sc
+    red = {}
+    for s in (16, 32, 64):
+        o = torch.empty(n // s, dtype=torch.float32, device="cuda")
+
+        def call():
+            k[0] += 1
+            tcu.segmented_reduce(xs[k[0] % 2], s, out=o, algo="tcgen05")
+        ms, _ = time_op(torch, call, 10, 3)
+        red[str(s)] = round(n / ms / 1e6, 1)
+    out["reduce"]["tcgen05"] = red
     out["note"] = ("direct launches, CUDA events around 10 back-to-back calls; the shuffle variant "
-                   "does not split inputs into exact parts (plain fp32 rounding)")
+                   "does not split inputs into exact parts (plain fp32 rounding); tcgen05 = "
+                   "tcgen05.mma with the accumulator in tensor memory, segment sizes 16/32/64 only")
     return out
 
 

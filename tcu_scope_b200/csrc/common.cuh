@@ -14,14 +14,14 @@ namespace tcu {
 // One CTA tile is what a single TMA bulk copy brings into one ring stage.  A
 // tile is cut into one contiguous slice per consumer warp.
 #ifndef TCU_STAGES
-#define TCU_STAGES 6
+#define TCU_STAGES 4
 #endif
 constexpr int kConsumerWarps = 8;
 constexpr int kSliceElems    = 2048;                         // halves per warp slice
 constexpr int kSliceBytes    = kSliceElems * 2;              // 4 KiB
 constexpr int kTileElems     = kSliceElems * kConsumerWarps; // 16384 halves per tile
 constexpr int kTileBytes     = kTileElems * 2;               // 32 KiB
-constexpr int kStages        = TCU_STAGES;                   // 6 stages = 192 KiB ring
+constexpr int kStages        = TCU_STAGES;                   // 4 stages = 128 KiB in flight per SM
 constexpr int kThreads       = (kConsumerWarps + 1) * 32;    // + 1 producer warp
 constexpr int kRingBytes     = kStages * kTileBytes;
 

@@ -266,7 +266,10 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
 #define TCU_SCAN_2CTA_MAX_CLASS 7
 #endif
 __host__ __device__ constexpr int scan_ctas_per_sm(int sc) { return sc <= TCU_SCAN_2CTA_MAX_CLASS ? 2 : 1; }
-__host__ __device__ constexpr int scan_stages(int sc) { return scan_ctas_per_sm(sc) == 1 ? kStages : 3; }
+#ifndef TCU_SCAN_2CTA_STAGES
+#define TCU_SCAN_2CTA_STAGES 3
+#endif
+__host__ __device__ constexpr int scan_stages(int sc) { return scan_ctas_per_sm(sc) == 1 ? kStages : TCU_SCAN_2CTA_STAGES; }
 __host__ __device__ constexpr int scan_dyn_smem_bytes(int sc) { return scan_stages(sc) * kTileBytes + 128; }
 
 template <int SC, bool OUT32>

@@ -10,7 +10,8 @@
 //       loaded by a swizzled tensor-map TMA copy (SWIZZLE_128B).
 //   B (16 x 64, K-major, same swizzle): B[n][k] = 1 iff k / S == n, built once
 //       in shared memory; column n of D is the sum of the n-th segment of a row.
-//   D (128 lanes x 16 fp32 columns of TMEM), double buffered.
+//   D (128 lanes x 16 fp32 columns of TMEM), a ring of accumulators deep enough
+//       to hide the MMA -> commit -> tcgen05.ld -> release round trip.
 //
 // Warps: 0 TMA producer, 1 MMA issuer (and TMEM owner), 2..5 epilogue.  Every
 // mbarrier wait is bounded; TMEM is released on every path out of the kernel.
@@ -24,11 +25,22 @@ namespace tcu {
 constexpr int kUmmaRows       = 128;                               // rows (TMEM lanes) per tile
 constexpr int kUmmaTileElems  = kUmmaRows * kSwizzleRowElems;      // 8192 halves
 constexpr int kUmmaTileBytes  = kUmmaTileElems * 2;                // 16 KiB
-constexpr int kUmmaStages     = 12;                                // 192 KiB of A tiles
+#ifndef TCU_UMMA_STAGES
+#define TCU_UMMA_STAGES 6
+#endif
+// Ring depth: 6 x 16 KiB in flight per SM measured fastest (1.03 of the copy
+// bandwidth at 2^28 elements); 8 stages give 0.98, 12 stages 0.90.
+constexpr int kUmmaStages     = TCU_UMMA_STAGES;
 constexpr int kUmmaN          = 16;                                // accumulator columns per tile
 constexpr int kUmmaBBytes     = kUmmaN * kSwizzleRowElems * 2;     // 2 KiB
 constexpr int kUmmaThreads    = 6 * 32;
-constexpr int kUmmaTmemCols   = 32;                                // two accumulators of 16 columns
+#ifndef TCU_UMMA_ACC_STAGES
+#define TCU_UMMA_ACC_STAGES 4
+#endif
+constexpr int kUmmaAccStages  = TCU_UMMA_ACC_STAGES;               // accumulators in flight (power of two)
+constexpr int kUmmaTmemCols   = kUmmaAccStages * kUmmaN < 32 ? 32 : kUmmaAccStages * kUmmaN;
+static_assert((kUmmaAccStages & (kUmmaAccStages - 1)) == 0 && kUmmaTmemCols <= 512 &&
+              (kUmmaTmemCols & (kUmmaTmemCols - 1)) == 0, "TMEM columns: a power of two, 32..512");
 constexpr int kUmmaDynSmemBytes = kUmmaStages * kUmmaTileBytes + kUmmaBBytes + 1024;
 
 // 64-bit shared-memory matrix descriptor, K-major, 128-byte swizzle: start
@@ -73,7 +85,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   static_assert(LOG2S >= 4 && LOG2S <= 6, "16, 32 or 64 elements per segment");
   constexpr int kSegsPerRow = kSwizzleRowElems >> LOG2S;  // 4, 2, 1 sums per 64-element row
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ __align__(8) uint64_t bars[2 * kUmmaStages + 4];
+  __shared__ __align__(8) uint64_t bars[2 * kUmmaStages + 2 * kUmmaAccStages];
   __shared__ uint32_t s_tmem_base;
   __shared__ uint32_t s_failed;
 
@@ -81,15 +93,16 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   uint8_t* bmat  = tiles + kUmmaStages * kUmmaTileBytes;  // 1 KiB aligned as well
   const uint32_t tiles_u32 = smem_u32(tiles), bmat_u32 = smem_u32(bmat);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kUmmaStages]);
-  const uint32_t tfull0 = smem_u32(&bars[2 * kUmmaStages]), tempty0 = tfull0 + 16;
+  const uint32_t tfull0 = smem_u32(&bars[2 * kUmmaStages]), tempty0 = tfull0 + 8 * kUmmaAccStages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
     for (int s = 0; s < kUmmaStages; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kUmmaAccStages; ++a) {
       mbar_init(tfull0 + 8 * a, 1);
       mbar_init(tempty0 + 8 * a, 4);  // one arrival per epilogue warp
     }
@@ -136,7 +149,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       uint32_t i = 0;
       for (unsigned long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
         const uint32_t s = i % kUmmaStages, ph = (i / kUmmaStages) & 1u;
-        const uint32_t a = i & 1u, aph = (i >> 1) & 1u;
+        const uint32_t a = i % kUmmaAccStages, aph = (i / kUmmaAccStages) & 1u;
         if (!mbar_wait(tempty0 + 8 * a, aph ^ 1u)) { s_failed = 1u; break; }  // accumulator drained
         if (!mbar_wait(full0 + 8 * s, ph)) { s_failed = 1u; break; }          // tile landed
         tcgen05_fence_after_sync();
@@ -155,7 +168,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     const bool out_f32 = p.out_is_f32 != 0;
     uint32_t i = 0;
     for (unsigned long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
-      const uint32_t a = i & 1u, aph = (i >> 1) & 1u;
+      const uint32_t a = i % kUmmaAccStages, aph = (i / kUmmaAccStages) & 1u;
       if (!mbar_wait(tfull0 + 8 * a, aph)) { s_failed = 1u; break; }
       tcgen05_fence_after_sync();
       uint32_t r0, r1, r2, r3;
