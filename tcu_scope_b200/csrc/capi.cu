@@ -482,10 +482,10 @@ int tcu_device_error(unsigned int* bits, int clear) {
 // debug build only: look-back timing counters (see scan_lookback_kernel.cuh)
 int tcu_debug_lookback_stats(unsigned long long* out8, int clear) {
   cudaDeviceSynchronize();
-  if (cudaMemcpyFromSymbol(out8, g_lb_stats, 64) != cudaSuccess) return TCU_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(out8, g_lb_stats, 128) != cudaSuccess) return TCU_ERR_CUDA;
   if (clear) {
-    unsigned long long z[8] = {0};
-    cudaMemcpyToSymbol(g_lb_stats, z, 64);
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(g_lb_stats, z, 128);
   }
   return TCU_OK;
 }

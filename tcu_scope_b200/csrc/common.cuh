@@ -90,6 +90,27 @@ __device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src_g
       : "memory");
 }
 
+// Linear TMA the other way: this CTA's shared memory -> global, tracked by the
+// issuing thread's bulk async-group.  Same alignment rules.
+__device__ __forceinline__ void tma_store_1d(void* dst_gmem, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(dst_gmem), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Returns once all but the newest kPending groups of this thread have finished
+// READING shared memory (their global writes may still be in flight).
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// Orders this thread's generic-proxy shared-memory writes before later
+// async-proxy (TMA, tensor core) reads of the same locations.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // Tiled TMA through a tensor map: one box of the 2-D view {64 halves, rows} of
 // the input lands in shared memory with the 128-byte swizzle applied (16-byte
 // chunk index XOR row index mod 8), which is what makes the scan kernels'

@@ -190,7 +190,7 @@ __device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const 
                                           const ScanOperands& ops, float& ch_lo, float& cl_lo,
                                           float& ch_hi, float& cl_hi, void* out,
                                           unsigned long long elem_base, int valid_elems, int g,
-                                          int t) {
+                                          int t, uint8_t* staged = nullptr) {
   using Geom = ScanGeom<SC>;
   // a new segment starts inside the row at this step: drop the carry
   if (SC == 4 || (SC == 5 && (j & 1) == 0) || (SC == 6 && (j & 3) == 0))
@@ -210,6 +210,13 @@ __device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const 
     cl_hi = nl.d2;
   }
   const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
+  if constexpr (!OUT32) {
+    if (staged != nullptr) {  // results replace the inputs in the ring stage; a bulk copy stores them
+      store4<false>(staged, e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0, hb.d1 + lb.d1);
+      store4<false>(staged, e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2, hb.d3 + lb.d3);
+      return;
+    }
+  }
   if (e_lo < valid_elems)
     store4<OUT32>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
                   hb.d1 + lb.d1);
@@ -257,19 +264,29 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
 
 // Segment classes as for the reduction: 4..11 = 2^class elements (inside one
 // slice), 12..14 = 4096/8192/16384 (2/4/8 slices of one tile).
-// Launch shape per class.  Classes up to 128 elements make one pass over the
-// slice and need few registers: two CTAs per SM (3-stage rings) double the
-// warps each scheduler can interleave, which is worth 5-9 % there.  From 256
-// elements on the slice is read once and kept in registers between the row
-// totals and the scan proper, which only fits with one CTA per SM.
+// Launch shape per class.  16-element segments have no carry and need few
+// registers: two CTAs per SM (3-stage rings) double the warps each scheduler
+// can interleave, worth 8 % there.  From 32 elements on the slice is read and
+// split once into registers (which frees the ring stage early and takes the
+// loads off the carry chain); that only fits with one CTA per SM, and measured
+// 7-23 % faster than two CTAs re-reading shared memory step by step.
 #ifndef TCU_SCAN_2CTA_MAX_CLASS
-#define TCU_SCAN_2CTA_MAX_CLASS 7
+#define TCU_SCAN_2CTA_MAX_CLASS 4
 #endif
 __host__ __device__ constexpr int scan_ctas_per_sm(int sc) { return sc <= TCU_SCAN_2CTA_MAX_CLASS ? 2 : 1; }
 #ifndef TCU_SCAN_2CTA_STAGES
 #define TCU_SCAN_2CTA_STAGES 3
 #endif
-__host__ __device__ constexpr int scan_stages(int sc) { return scan_ctas_per_sm(sc) == 1 ? kStages : TCU_SCAN_2CTA_STAGES; }
+#ifndef TCU_SCAN_TMA_STORE
+#define TCU_SCAN_TMA_STORE 6  // largest class whose fp16 outputs leave through shared memory
+#endif
+#ifndef TCU_SCAN_BULK_STAGES
+#define TCU_SCAN_BULK_STAGES 5  // those classes hold a stage one tile longer
+#endif
+__host__ __device__ constexpr int scan_stages(int sc) {
+  return scan_ctas_per_sm(sc) == 2 ? TCU_SCAN_2CTA_STAGES
+                                   : (sc <= TCU_SCAN_TMA_STORE ? TCU_SCAN_BULK_STAGES : kStages);
+}
 __host__ __device__ constexpr int scan_dyn_smem_bytes(int sc) { return scan_stages(sc) * kTileBytes + 128; }
 
 template <int SC, bool OUT32>
@@ -277,6 +294,10 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
   static_assert(SC >= 4 && SC <= 14, "the look-back class has its own kernel");
   constexpr int kStages = scan_stages(SC);  // shadows the library-wide ring depth
   constexpr bool kScanCache = scan_ctas_per_sm(SC) == 1;  // slice kept in registers between passes
+  // fp16 outputs of a slice overwrite its inputs in the ring stage and leave
+  // through one bulk copy per warp; the stage is released one tile later, once
+  // that copy has read it.
+  constexpr bool kBulkStore = !OUT32 && kScanCache && SC <= TCU_SCAN_TMA_STORE;
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kStages];
   __shared__ float2 part[2][kConsumerWarps];
@@ -349,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
         }
       }
     }
-    if constexpr (kScanCache) {
+    if constexpr (kScanCache && !kBulkStore) {
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);  // everything needed is in registers
     }
@@ -386,13 +407,29 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
       for (int j = 0; j < 8; ++j) {
         if constexpr (!kScanCache) load_split(addr, j, ah[0], al[0]);  // second read
         scan_step<SC, OUT32>(j, ah[kScanCache ? j : 0], al[kScanCache ? j : 0], ops, ch_lo, cl_lo,
-                             ch_hi, cl_hi, p.out, elem_base, valid_elems, g, t);
+                             ch_hi, cl_hi, p.out, elem_base, valid_elems, g, t,
+                             kBulkStore ? slice : nullptr);
+      }
+    }
+    if constexpr (kBulkStore) {
+      fence_proxy_async_smem();  // the generic-proxy writes above, before the bulk copy reads them
+      __syncwarp();
+      if (lane == 0) {
+        if (active)
+          tma_store_1d(static_cast<uint8_t*>(p.out) + slice_off, smem_u32(slice),
+                       static_cast<uint32_t>(valid_bytes));
+        bulk_commit_group();
+        bulk_wait_group_read<1>();  // the previous tile's copy has read its stage
+        if (i > 0) mbar_arrive(empty0 + 8 * ((i - 1) % kStages));
       }
     }
     if constexpr (!kScanCache) {
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }
+  }
+  if constexpr (kBulkStore) {
+    if (lane == 0) bulk_wait_group_read<0>();  // shared memory must outlive the copies that read it
   }
 }
 

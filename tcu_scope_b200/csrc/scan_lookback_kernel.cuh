@@ -65,7 +65,10 @@ constexpr uint32_t kNoEnd = 0xffffffffu;
 // debug counters (ns): [0] look-back time sum [1] tiles [2] look-back max
 // [3] pass-2 warp 8 wait for resolved  [4] pass-1 warp 0 wait for full  [5] pass-1 compute
 // [6] pass-2 compute  [7] producer wait for empty
-__device__ unsigned long long g_lb_stats[8];
+// [8] in-block walk ns [9] block walk ns [10] in-block empty polls [11] block empty polls
+// [12] ns from the tile's ticket to the start of its look-back
+__device__ unsigned long long g_lb_stats[16];
+__device__ unsigned long long g_lb_polls_scratch;
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -110,6 +113,9 @@ __device__ __forceinline__ double look_back(const unsigned long long* status, lo
   double sum     = 0.0;
   uint32_t polls = 0;
   found_inclusive = false;
+#ifdef TCU_LB_PROFILE
+  const bool use_prefetched_slot = use_prefetched;  // block-level walks are the prefetched ones
+#endif
   while (last >= first) {
     const long long idx = last - lane;
     const bool valid    = idx >= first;
@@ -134,6 +140,9 @@ __device__ __forceinline__ double look_back(const unsigned long long* status, lo
     }
     last -= take;
     if (take == 0) {  // the nearest word is still empty: wait for its tile, but not forever
+#ifdef TCU_LB_PROFILE
+      if (lane == 0) atomicAdd(&g_lb_stats[status == nullptr ? 10 : 10 + (int)use_prefetched_slot], 1ull);
+#endif
       if (++polls > kPollAttempts) {
         if (lane == 0) raise_error(kErrLookbackTimeout);
         return sum;  // wrong result, flagged, but no hang
@@ -279,6 +288,10 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
         bool complete = false;
         const double in_block = look_back(p.tile_status, (long long)tile - 1,
                                           (long long)blk_first, lane, complete);
+#ifdef TCU_LB_PROFILE
+        const unsigned long long lb_t1 = gtime();
+        if (lane == 0) atomicAdd(&g_lb_stats[8], lb_t1 - lb_t0);
+#endif
         double before_block = 0.0;
         if (!complete) {  // blk > 0 here: block 0 starts with the segment's inclusive first tile
           if (closes_block && lane == 0)
@@ -288,6 +301,9 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
                                    /*use_prefetched=*/true, blk_word);
         }
         excl = before_block + in_block;
+#ifdef TCU_LB_PROFILE
+        if (lane == 0) atomicAdd(&g_lb_stats[9], gtime() - lb_t1);
+#endif
         if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
       }
       // the last tile of a block publishes the prefix through the block
