@@ -64,15 +64,26 @@ __device__ __forceinline__ ScanOperands make_scan_operands(int lane, bool exclus
   return o;
 }
 
-template <bool OUT32>
+// kStream: the lines are not read again by this kernel -- mark them as the
+// first to leave L2 (st.global.cs), so that they do not displace data that is.
+template <bool OUT32, bool kStream = false>
 __device__ __forceinline__ void store4(void* out, unsigned long long idx, float r0, float r1,
                                        float r2, float r3) {
   if constexpr (OUT32) {
-    *reinterpret_cast<float4*>(static_cast<float*>(out) + idx) = make_float4(r0, r1, r2, r3);
+    float* dst = static_cast<float*>(out) + idx;
+    if constexpr (kStream)
+      asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};"
+                   ::"l"(dst), "f"(r0), "f"(r1), "f"(r2), "f"(r3) : "memory");
+    else
+      *reinterpret_cast<float4*>(dst) = make_float4(r0, r1, r2, r3);
   } else {
     const __half2 a = __floats2half2_rn(r0, r1), b = __floats2half2_rn(r2, r3);
-    *reinterpret_cast<uint2*>(static_cast<__half*>(out) + idx) =
-        make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+    const uint32_t ua = *reinterpret_cast<const uint32_t*>(&a), ub = *reinterpret_cast<const uint32_t*>(&b);
+    __half* dst = static_cast<__half*>(out) + idx;
+    if constexpr (kStream)
+      asm volatile("st.global.cs.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(ua), "r"(ub) : "memory");
+    else
+      *reinterpret_cast<uint2*>(dst) = make_uint2(ua, ub);
   }
 }
 
@@ -233,7 +244,7 @@ struct RowCarry {
   float h_lo, l_lo, h_hi, l_hi;  // (exact hi part, lo part) x (row g, row g+8)
 };
 
-template <int SC, bool OUT32>
+template <int SC, bool OUT32, bool kStream = false>
 __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah)[4],
                                                       const uint32_t (&al)[4],
                                                       const ScanOperands& ops, RowCarry& c,
@@ -255,10 +266,10 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
   }
   const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
   if (e_lo < valid_elems)
-    store4<OUT32>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
+    store4<OUT32, kStream>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
                   hb.d1 + lb.d1);
   if (e_hi < valid_elems)
-    store4<OUT32>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
+    store4<OUT32, kStream>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
                   hb.d3 + lb.d3);
 }
 

@@ -12,53 +12,65 @@
 // that every predecessor of a tile already belongs to a running CTA: a wait
 // can only be on work that is making progress.  Every poll loop is bounded.
 //
-// Inside a CTA the look-back is taken off the critical path.  Tile i goes
-//   producer:  TMA load                               -> full[s]
-//   consumers: pass 1 (slice totals, row carries)     -> p1done[s]
-//   one of 4 look-back warps: publish aggregate, walk back, publish prefix
-//                                                     -> resolved[s]
-//   consumers: pass 2 (the scan, seeded), stores      -> empty[s]
-// and the consumers run pass 1 kLookahead tiles ahead of pass 2, so that a
-// tile's aggregate is public long before its successors need it and several
-// look-backs per CTA are in flight while the tensor cores stay busy.
+// A tile's prefix is known only when every earlier tile of the machine has
+// been loaded and summed, several microseconds after its own load -- more
+// data than shared memory can hold at full bandwidth.  So a tile is not kept
+// on chip while it waits: it is loaded twice, the second time out of L2.
+//   producer A: ticket, TMA load (L2 evict-last)       -> fullA[a]
+//   pass-1 warps: slice totals, row carries (kept in a small queue slot q)
+//                                                      -> p1done[q], emptyA[a]
+//   one of the look-back warps: publish aggregate, walk back, publish prefix
+//                                                      -> resolved[q]
+//   producer B: waits for resolved[q], loads the tile again (L2 evict-first)
+//                                                      -> fullB[b]
+//   pass-2 warps: the scan, seeded; stores             -> emptyB[b], qfree[q]
+// Ring A only ever holds tiles in flight or being summed, ring B only tiles
+// whose prefix is already known; what waits for a look-back is a 4 KiB queue
+// slot, not a 32 KiB tile.
 #pragma once
 
 #include "scan_kernels.cuh"
 
 namespace tcu {
 
-#ifndef TCU_LB_STAGES
-#define TCU_LB_STAGES 6
+#ifndef TCU_LB_STREAM_STORES
+#define TCU_LB_STREAM_STORES 1
 #endif
-#ifndef TCU_LB_SAVE_CARRIES
-#define TCU_LB_SAVE_CARRIES 1
+#ifndef TCU_LB_RING_A
+#define TCU_LB_RING_A 2
 #endif
-constexpr int kLookbackStages       = TCU_LB_STAGES;
-constexpr bool kSaveCarries         = TCU_LB_SAVE_CARRIES != 0;
-#ifndef TCU_LOOKAHEAD
-#define TCU_LOOKAHEAD 4
+#ifndef TCU_LB_RING_B
+#define TCU_LB_RING_B 3
 #endif
-constexpr int kLookahead            = TCU_LOOKAHEAD;  // pass 1 runs this many tiles ahead of pass 2
+#ifndef TCU_LB_QUEUE
+#define TCU_LB_QUEUE 10
+#endif
+constexpr int kRingA = TCU_LB_RING_A;  // stages of the first-read ring
+constexpr int kRingB = TCU_LB_RING_B;  // stages of the second-read ring
+constexpr int kQueue = TCU_LB_QUEUE;   // tiles between their first and second read, per CTA
 #ifndef TCU_LB_WARPS
 #define TCU_LB_WARPS 6
 #endif
 constexpr int kLookbackWarps        = TCU_LB_WARPS;
-// A look-back warp's first tile must be in the first pass over the ring: a
+// A look-back warp's first tile must be in the first pass over the queue: a
 // wait for a later phase on a fresh barrier would fall through.
-static_assert(kLookbackWarps <= kLookbackStages, "at most one look-back warp per ring stage");
+static_assert(kLookbackWarps <= kQueue, "at most one look-back warp per queue slot");
 constexpr int kLookbackCtasPerSm    = 1;
-// Warp roles: [0,8) pass-1 warps, [8,16) pass-2 warps, 16 producer, 17.. look-back.
-// Pass 1 and pass 2 of different tiles run at the same time on different warps:
-// twice the warps to interleave on each scheduler, which is what the dependent
-// MMA / shuffle chains of the two passes need to keep the issue slots busy.
+// Warp roles: [0,8) pass 1, [8,16) pass 2, 16 producer A, 17 producer B, 18.. look-back.
 constexpr int kPass2Warp0           = kConsumerWarps;
-constexpr int kProducerWarp         = 2 * kConsumerWarps;
-constexpr int kLookbackWarp0        = kProducerWarp + 1;
-constexpr int kLookbackThreads      = (2 * kConsumerWarps + 1 + kLookbackWarps) * 32;
-// one float4 (row carries) per consumer lane, kept from pass 1 to pass 2
-constexpr int kCarryBytesPerStage   = kSaveCarries ? kConsumerWarps * 32 * 16 : 0;
+constexpr int kProducerAWarp        = 2 * kConsumerWarps;
+constexpr int kProducerBWarp        = kProducerAWarp + 1;
+constexpr int kLookbackWarp0        = kProducerBWarp + 1;
+constexpr int kLookbackThreads      = (2 * kConsumerWarps + 2 + kLookbackWarps) * 32;
+#ifndef TCU_LB_SAVE_CARRIES
+#define TCU_LB_SAVE_CARRIES 1
+#endif
+// one float4 (row carries) per pass-1 lane, kept from pass 1 to pass 2 -- or
+// nothing, and pass 2 sums the rows of its slice again
+constexpr bool kSaveCarries         = TCU_LB_SAVE_CARRIES != 0;
+constexpr int kCarryBytesPerSlot    = kSaveCarries ? kConsumerWarps * 32 * 16 : 0;
 constexpr int kLookbackDynSmemBytes =
-    kLookbackStages * (kTileBytes + kCarryBytesPerStage) + 1024;
+    (kRingA + kRingB) * kTileBytes + kQueue * kCarryBytesPerSlot + 1024;
 constexpr uint32_t kNoEnd = 0xffffffffu;
 
 #ifdef TCU_LB_PROFILE
@@ -183,30 +195,41 @@ template <bool OUT32, bool kSwz>
 __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     scan_lookback_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tmap) {
   constexpr int SC = 15;  // row-stream geometry, rows always chained
-  constexpr int NS = kLookbackStages;
+  constexpr int NA = kRingA, NB = kRingB, NQ = kQueue;
   extern __shared__ uint8_t dyn_smem[];
-  __shared__ __align__(8) uint64_t bars[4 * NS];  // full | p1done | resolved | empty
-  __shared__ unsigned long long stage_tile[NS];
-  __shared__ float2 part[NS][kConsumerWarps];      // slice totals (exact hi, lo)
-  __shared__ double tile_excl[NS];                 // exclusive prefix of the tile in its segment
+  // fullA | emptyA | fullB | emptyB | p1done | resolved | qfree
+  __shared__ __align__(8) uint64_t bars[2 * NA + 2 * NB + 3 * NQ];
+  __shared__ unsigned long long slot_tile[NQ];
+  __shared__ float2 part[NQ][kConsumerWarps];      // slice totals (exact hi, lo)
+  __shared__ double tile_excl[NQ];                 // exclusive prefix of the tile in its segment
   __shared__ uint32_t s_abort, s_end_index;
 
-  // 1 KiB-aligned ring: the swizzle pattern repeats every 1024 bytes
-  uint8_t* ring = dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u);
-  float4* carries = reinterpret_cast<float4*>(ring + NS * kTileBytes);  // [NS][8][32]
-  const uint32_t ring_u32 = smem_u32(ring);
-  const uint32_t full0 = smem_u32(&bars[0]), p1done0 = smem_u32(&bars[NS]),
-                 resolved0 = smem_u32(&bars[2 * NS]), empty0 = smem_u32(&bars[3 * NS]);
+  // 1 KiB-aligned rings: the swizzle pattern repeats every 1024 bytes
+  uint8_t* ring_a = dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u);
+  uint8_t* ring_b = ring_a + NA * kTileBytes;
+  float4* carries = reinterpret_cast<float4*>(ring_b + NB * kTileBytes);  // [NQ][8][32]
+  const uint32_t ring_a_u32 = smem_u32(ring_a), ring_b_u32 = smem_u32(ring_b);
+  const uint32_t full_a0 = smem_u32(&bars[0]), empty_a0 = full_a0 + 8 * NA;
+  const uint32_t full_b0 = empty_a0 + 8 * NA, empty_b0 = full_b0 + 8 * NB;
+  const uint32_t p1done0 = empty_b0 + 8 * NB, resolved0 = p1done0 + 8 * NQ,
+                 qfree0 = resolved0 + 8 * NQ;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* abort_flag = &s_abort;
   volatile uint32_t* end_index  = &s_end_index;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(p1done0 + 8 * s, kConsumerWarps);
-      mbar_init(resolved0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, kConsumerWarps);
+    for (int a = 0; a < NA; ++a) {
+      mbar_init(full_a0 + 8 * a, 1);
+      mbar_init(empty_a0 + 8 * a, kConsumerWarps);
+    }
+    for (int b = 0; b < NB; ++b) {
+      mbar_init(full_b0 + 8 * b, 1);
+      mbar_init(empty_b0 + 8 * b, kConsumerWarps);
+    }
+    for (int q = 0; q < NQ; ++q) {
+      mbar_init(p1done0 + 8 * q, kConsumerWarps);
+      mbar_init(resolved0 + 8 * q, 1);
+      mbar_init(qfree0 + 8 * q, kConsumerWarps);
     }
     s_abort     = 0u;
     s_end_index = kNoEnd;
@@ -218,34 +241,55 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   const unsigned long long total_bytes = p.num_elems * 2ull;
   const unsigned long long num_tiles   = (total_bytes + kTileBytes - 1) / kTileBytes;
 
-  if (warp == kProducerWarp) {
-    // ------------------------------------------------------------ producer
+  // one tile into one ring stage, by either kind of copy
+  auto load_tile = [&](uint32_t dst, unsigned long long tile, uint32_t bar, uint64_t policy) {
+    const unsigned long long off = tile * kTileBytes;
+    const unsigned long long rem = total_bytes - off;
+    const uint32_t bytes = rem < (unsigned long long)kTileBytes ? (uint32_t)rem : kTileBytes;
+    if constexpr (kSwz) {
+      // the whole box always arrives: rows past the end of the array come as zeros
+      mbar_arrive_expect_tx(bar, kTileBytes);
+      tma_load_2d_hint(dst, &tmap, 0, (int)(tile * kTileRows), bar, policy);
+    } else {
+      mbar_arrive_expect_tx(bar, bytes);
+      tma_load_1d_hint(dst, p.in + off, bytes, bar, policy);
+    }
+  };
+
+  if (warp == kProducerAWarp) {
+    // ---------------------------------------------------------- producer A
     if (lane == 0) {
+      const uint64_t keep = l2_policy_evict_last();  // the tile is read again within microseconds
       for (uint32_t i = 0;; ++i) {
-        const uint32_t s = i % NS, ph = (i / NS) & 1u;
+        const uint32_t a = i % NA, q = i % NQ;
         {
           LB_T0();
-          if (!mbar_wait_or_stop(empty0 + 8 * s, ph ^ 1u, abort_flag, nullptr, 0)) break;
+          if (!mbar_wait_or_stop(qfree0 + 8 * q, ((i / NQ) & 1u) ^ 1u, abort_flag, nullptr, 0)) break;
+          if (!mbar_wait_or_stop(empty_a0 + 8 * a, ((i / NA) & 1u) ^ 1u, abort_flag, nullptr, 0)) break;
           LB_ADD(7, true);
         }
         const unsigned long long tile = atomicAdd(p.ticket, 1u);
         if (tile >= num_tiles) {
-          stage_tile[s] = kTileEnd;
-          mbar_arrive(full0 + 8 * s);  // release: the consumers see the end marker
+          slot_tile[q] = kTileEnd;
+          mbar_arrive(full_a0 + 8 * a);  // release: the pass-1 warps see the end marker
           break;
         }
-        stage_tile[s] = tile;
-        const unsigned long long off = tile * kTileBytes;
-        const unsigned long long rem = total_bytes - off;
-        const uint32_t bytes = rem < (unsigned long long)kTileBytes ? (uint32_t)rem : kTileBytes;
-        if constexpr (kSwz) {
-          // the whole box always arrives: rows past the end of the array come as zeros
-          mbar_arrive_expect_tx(full0 + 8 * s, kTileBytes);
-          tma_load_2d(ring_u32 + s * kTileBytes, &tmap, 0, (int)(tile * kTileRows), full0 + 8 * s);
-        } else {
-          mbar_arrive_expect_tx(full0 + 8 * s, bytes);
-          tma_load_1d(ring_u32 + s * kTileBytes, p.in + off, bytes, full0 + 8 * s);
-        }
+        slot_tile[q] = tile;
+        load_tile(ring_a_u32 + a * kTileBytes, tile, full_a0 + 8 * a, keep);
+      }
+    }
+    return;
+  }
+
+  if (warp == kProducerBWarp) {
+    // ---------------------------------------------------------- producer B
+    if (lane == 0) {
+      const uint64_t drop = l2_policy_evict_first();  // last use of these lines
+      for (uint32_t k = 0;; ++k) {
+        const uint32_t b = k % NB, q = k % NQ;
+        if (!mbar_wait_or_stop(resolved0 + 8 * q, (k / NQ) & 1u, abort_flag, end_index, k)) break;
+        if (!mbar_wait_or_stop(empty_b0 + 8 * b, ((k / NB) & 1u) ^ 1u, abort_flag, nullptr, 0)) break;
+        load_tile(ring_b_u32 + b * kTileBytes, slot_tile[q], full_b0 + 8 * b, drop);
       }
     }
     return;
@@ -254,13 +298,13 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   if (warp >= kLookbackWarp0) {
     // ------------------------------------------------------ look-back warps
     for (uint32_t i = warp - kLookbackWarp0;; i += kLookbackWarps) {
-      const uint32_t s = i % NS, ph = (i / NS) & 1u;
-      if (!mbar_wait_or_stop(p1done0 + 8 * s, ph, abort_flag, end_index, i)) break;
-      const unsigned long long tile = stage_tile[s];
+      const uint32_t q = i % NQ, ph = (i / NQ) & 1u;
+      if (!mbar_wait_or_stop(p1done0 + 8 * q, ph, abort_flag, end_index, i)) break;
+      const unsigned long long tile = slot_tile[q];
       LB_T0();
       double agg = 0.0;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) agg += (double)part[s][w].x + (double)part[s][w].y;
+      for (int w = 0; w < kConsumerWarps; ++w) agg += (double)part[q][w].x + (double)part[q][w].y;
       // Two levels: tiles inside a block of kBlockTiles tiles, then whole blocks
       // (block b of a segment = tiles [seg_first + b*32, +32)).  A walk is at
       // most one window inside the block plus about one window over blocks,
@@ -310,8 +354,8 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       if (closes_block && lane == 0)
         status_store(p.block_status + blk_base + blk, excl + agg, kStateInclusive);
       if (lane == 0) {
-        tile_excl[s] = excl;
-        mbar_arrive(resolved0 + 8 * s);  // release: tile_excl is visible to the waiters
+        tile_excl[q] = excl;
+        mbar_arrive(resolved0 + 8 * q);  // release: tile_excl is visible to the waiters
 #ifdef TCU_LB_PROFILE
         const unsigned long long dt = gtime() - lb_t0;
         atomicAdd(&g_lb_stats[0], dt);
@@ -335,9 +379,9 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     unsigned long long slice_off;
     int valid_bytes;
   };
-  auto slice_view = [&](uint32_t s, unsigned long long tile) {
+  auto slice_view = [&](uint8_t* stage, unsigned long long tile) {
     SliceView v;
-    v.slice     = ring + s * kTileBytes + cw * kSliceBytes;
+    v.slice     = stage + cw * kSliceBytes;
     v.slice_off = tile * kTileBytes + (unsigned long long)cw * kSliceBytes;
     const long long left = (long long)total_bytes - (long long)v.slice_off;
     v.valid_bytes = left <= 0 ? 0 : (left < kSliceBytes ? (int)left : kSliceBytes);
@@ -346,19 +390,19 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
 
   // pass 1 of local tile i: slice total and row carries.  false = no such tile.
   auto pass1 = [&](uint32_t i) -> bool {
-    const uint32_t s = i % NS, ph = (i / NS) & 1u;
+    const uint32_t a = i % NA, q = i % NQ;
     {
       LB_T0();
-      if (!mbar_wait_or_stop(full0 + 8 * s, ph, abort_flag, nullptr, 0)) return false;
+      if (!mbar_wait_or_stop(full_a0 + 8 * a, (i / NA) & 1u, abort_flag, nullptr, 0)) return false;
       LB_ADD(4, threadIdx.x == 0);
     }
     LB_T0();
-    const unsigned long long tile = stage_tile[s];
+    const unsigned long long tile = slot_tile[q];
     if (tile == kTileEnd) {
-      if (lane == 0) *end_index = i;  // lets the look-back warps leave
+      if (lane == 0) *end_index = i;  // lets producer B, the look-back and the pass-2 warps leave
       return false;
     }
-    const SliceView v = slice_view(s, tile);
+    const SliceView v = slice_view(ring_a + a * kTileBytes, tile);
     const bool active = v.valid_bytes > 0;
     if constexpr (!kSwz)
       if (active && v.valid_bytes < kSliceBytes) zero_slice_tail(v.slice, v.valid_bytes, lane);
@@ -376,30 +420,33 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     float ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l;
     row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
     if constexpr (kSaveCarries)
-      carries[(s * kConsumerWarps + cw) * 32 + lane] = make_float4(ch_lo, cl_lo, ch_hi, cl_hi);
-    if (lane == 0) part[s][cw] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
+      carries[(q * kConsumerWarps + cw) * 32 + lane] = make_float4(ch_lo, cl_lo, ch_hi, cl_hi);
+    if (lane == 0) part[q][cw] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
     __syncwarp();
-    if (lane == 0) mbar_arrive(p1done0 + 8 * s);
+    if (lane == 0) {
+      mbar_arrive(p1done0 + 8 * q);
+      mbar_arrive(empty_a0 + 8 * a);  // the stage can take the next first read
+    }
     LB_ADD(5, threadIdx.x == 0);
     return true;
   };
 
   // pass 2 of local tile k: the scan proper, seeded with everything before the slice
   auto pass2 = [&](uint32_t k) -> bool {
-    const uint32_t s = k % NS, ph = (k / NS) & 1u;
-    // the tile landed long ago (pass 1 has read it); this wait returns at once and makes the
-    // copy's bytes visible to this warp as well
+    const uint32_t b = k % NB, q = k % NQ;
     {
       LB_T0();
-      if (!mbar_wait_or_stop(full0 + 8 * s, ph, abort_flag, end_index, k)) return false;
-      if (!mbar_wait_or_stop(resolved0 + 8 * s, ph, abort_flag, end_index, k)) return false;
+      // producer B loads the tile only after its look-back; the second wait returns at once
+      // and makes tile_excl visible to this warp as well
+      if (!mbar_wait_or_stop(full_b0 + 8 * b, (k / NB) & 1u, abort_flag, end_index, k)) return false;
+      if (!mbar_wait_or_stop(resolved0 + 8 * q, (k / NQ) & 1u, abort_flag, end_index, k)) return false;
       LB_ADD(3, threadIdx.x == kPass2Warp0 * 32);
     }
     LB_T0();
-    const unsigned long long tile = stage_tile[s];
-    const SliceView v = slice_view(s, tile);
-    double carry = tile_excl[s];
-    for (int w = 0; w < cw; ++w) carry += (double)part[s][w].x + (double)part[s][w].y;
+    const unsigned long long tile = slot_tile[q];
+    const SliceView v = slice_view(ring_b + b * kTileBytes, tile);
+    double carry = tile_excl[q];
+    for (int w = 0; w < cw; ++w) carry += (double)part[q][w].x + (double)part[q][w].y;
     // Everything before this slice, as two floats that ride through the MMAs'
     // accumulator operand with the row carries: xh a multiple of 2^-13 (what the
     // hi parts are made of, so sums below 2^11 stay exact), xl the small rest.
@@ -407,12 +454,13 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     const float xh = (float)carry_hi;
     const float xl = (float)(carry - (double)xh);
     if (v.valid_bytes > 0) {
-      float ch_lo, cl_lo, ch_hi, cl_hi;
+      if constexpr (!kSwz)
+        if (v.valid_bytes < kSliceBytes) zero_slice_tail(v.slice, v.valid_bytes, lane);
       const SliceAddr<Geom, kSwz> addr(v.slice, g, t);
+      float4 c;
       if constexpr (kSaveCarries) {
-        const float4 c = carries[(s * kConsumerWarps + cw) * 32 + lane];
-        ch_lo = c.x, cl_lo = c.y, ch_hi = c.z, cl_hi = c.w;
-      } else {  // no room to keep them: redo the row totals
+        c = carries[(q * kConsumerWarps + cw) * 32 + lane];
+      } else {
         Acc tot_h = zero, tot_l = zero;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -422,20 +470,24 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
           tot_l = mma_ones(al, tot_l);
         }
         float slice_h, slice_l;
-        row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
+        row_carries<16>(tot_h, tot_l, g, c.x, c.y, c.z, c.w, slice_h, slice_l);
       }
-      RowCarry rc{ch_lo + xh, cl_lo + xl, ch_hi + xh, cl_hi + xl};
+      RowCarry rc{c.x + xh, c.y + xl, c.z + xh, c.w + xl};
       const unsigned long long elem_base = v.slice_off / 2;
       const int valid_elems = v.valid_bytes / 2;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
         load_split(addr, j, ah, al);
-        scan_step_independent<SC, OUT32>(j, ah, al, ops, rc, p.out, elem_base, valid_elems, g, t);
+        scan_step_independent<SC, OUT32, TCU_LB_STREAM_STORES != 0>(j, ah, al, ops, rc, p.out, elem_base,
+                                                                    valid_elems, g, t);
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    if (lane == 0) {
+      mbar_arrive(empty_b0 + 8 * b);
+      mbar_arrive(qfree0 + 8 * q);  // slot_tile, part, carries and tile_excl of the slot are free
+    }
     LB_ADD(6, threadIdx.x == kPass2Warp0 * 32);
     return true;
   };
