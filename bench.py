@@ -44,7 +44,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--algo", default="auto", choices=["auto", "mma", "shuffle"])
+    ap.add_argument("--algo", default="auto", choices=["auto", "mma", "shuffle", "tcgen05"],
+                    help="tcgen05 only exists for segment sizes 16/32/64: use it with --profile reduce")
     ap.add_argument("--log2-elems", type=int, default=LOG2_ELEMS,
                     help="elements per GPU (default 28, the reference sweep's size)")
     ap.add_argument("--profile", default=None, choices=["reduce", "scan", "full"],
@@ -52,7 +53,11 @@ def parse_args():
                          "(the small case an ncu capture wraps)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other configurations, the e2e leg and the CPU baseline")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.algo == "tcgen05" and args.profile != "reduce":
+        ap.error("--algo tcgen05 covers segment sizes 16/32/64 only: use it with --profile reduce "
+                 "(the timed sweep reports it under ablation_tensor_core_vs_shuffle)")
+    return args
 
 
 def hbm_peak():
@@ -509,7 +514,7 @@ def profile_pass(torch, tcu, args, n, json_fd):
     """One launch of each kernel of a family, for a profiler to capture."""
     x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024, 0)
     if args.profile == "reduce":
-        for s in SWEEP:
+        for s in (SWEEP if args.algo != "tcgen05" else (16, 32, 64)):
             tcu.segmented_reduce(x, s, algo=args.algo)
     elif args.profile == "scan":
         for s, dt in [(16, torch.float16), (256, torch.float16), (4096, torch.float32)]:

@@ -35,6 +35,7 @@ constexpr unsigned kErrLookbackTimeout = 2u;  // a tile-status poll ran out
 constexpr uint32_t kWaitHintNs   = 1000;
 constexpr uint32_t kWaitAttempts = 1u << 21;
 constexpr uint32_t kPollAttempts = 1u << 22;  // tile-status polls (each ~0.5 us)
+constexpr uint32_t kSpinAttempts = 1u << 24;  // shared-memory flag polls between warps of a CTA
 
 __device__ unsigned int g_error_word;  // sticky until cleared by the host
 
@@ -88,6 +89,16 @@ __device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src_g
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
       ::"r"(dst_smem), "l"(src_gmem), "r"(bytes), "r"(bar)
       : "memory");
+}
+
+// Flag hand-off between warps of one CTA through shared memory.
+__device__ __forceinline__ void st_release_cta(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_cta(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
 }
 
 // Linear TMA the other way: this CTA's shared memory -> global, tracked by the

@@ -311,7 +311,19 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
   constexpr bool kBulkStore = !OUT32 && kScanCache && SC <= TCU_SCAN_TMA_STORE;
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kStages];
-  __shared__ float2 part[2][kConsumerWarps];
+#ifndef TCU_SCAN_P2P
+#define TCU_SCAN_P2P 1
+#endif
+  // Slice totals cross warps either under a barrier of all consumer warps, or
+  // (fp16 outputs) point to point: a warp publishes its total with a sequence
+  // number and only the later warps of the same segment wait for it, so the
+  // eight warps do not fall into lock step.  A warp cannot be more than kStages
+  // tiles ahead of the slowest one (stages are released by all eight), so
+  // 2 * kStages slots are never overwritten while still being read.
+  constexpr bool kP2P = SC >= 12 && !OUT32 && TCU_SCAN_P2P != 0;
+  constexpr int kPartSlots = kP2P ? 2 * kStages : 2;
+  __shared__ float2 part[kPartSlots][kConsumerWarps];
+  __shared__ uint32_t part_seq[kPartSlots][kConsumerWarps];
 
   uint8_t* ring = dyn_smem + ((128u - (smem_u32(dyn_smem) & 127u)) & 127u);
   const uint32_t ring_u32 = smem_u32(ring);
@@ -325,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
     }
     mbar_fence_init();
   }
+  if (threadIdx.x < kPartSlots * kConsumerWarps) (&part_seq[0][0])[threadIdx.x] = 0u;
   __syncthreads();
   pdl_prologue();  // nothing above touched global memory
 
@@ -394,13 +407,28 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
       float slice_h, slice_l;
       row_carries<kRowsPerSeg>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
       if constexpr (SC >= 12) {
-        if (lane == 0)
-          part[i & 1][warp] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
-        consumer_sync();
         constexpr int kWarpsPerSeg = 1 << (SC - 11);  // 2, 4, 8
         const int w0 = warp & ~(kWarpsPerSeg - 1);
+        const uint32_t slot = i % kPartSlots;
+        if (lane == 0)
+          part[slot][warp] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
+        if constexpr (kP2P) {
+          if (lane == 0) st_release_cta(&part_seq[slot][warp], i + 1u);
+          // lane k waits for the k-th earlier warp of the segment
+          bool ready = w0 + lane >= warp;
+          for (uint32_t spin = 0; !__all_sync(0xffffffffu, ready); ++spin) {
+            if (!ready) ready = ld_acquire_cta(&part_seq[slot][w0 + lane]) == i + 1u;
+            if (spin > kSpinAttempts) {  // a warp of this CTA died: flag it, results are wrong
+              if (lane == 0) raise_error(kErrBarrierTimeout);
+              dead = true;
+              break;
+            }
+          }
+        } else {
+          consumer_sync();
+        }
         for (int w = w0; w < warp; ++w) {
-          const float2 pr = part[i & 1][w];
+          const float2 pr = part[slot][w];
           xh += pr.x;
           xl += pr.y;
         }
