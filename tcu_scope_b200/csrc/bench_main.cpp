@@ -114,6 +114,22 @@ void add_tune(std::vector<Benchmark>& out, const std::string& base, int op, size
     }
 }
 
+// Fixed-size kernels carry two template arguments, <SEGMENTS_PER_WARP, WARPS_PER_BLOCK>
+// (src/reduction/seg_wmma_16.cu:132-147, seg_wmma_256.cu; same in src/prefixsum).
+void add_fixed(std::vector<Benchmark>& out, const Options& o, const std::string& base, int op,
+               size_t s) {
+  for (int spw : {1, 2, 4, 8})
+    for (int wpb : {1, 2, 4, 8})
+      for (int l = o.min_log2; l <= o.max_log2; ++l) {
+        const size_t n = size_t(1) << l;
+        if (n < s) continue;
+        out.push_back({base + "<" + std::to_string(spw) + ", " + std::to_string(wpb) +
+                           ">/num_segments:" + std::to_string(n / s) + "/segment_size:" +
+                           std::to_string(s) + "/num_elements:" + std::to_string(n) + "/manual_time",
+                       op, n / s, s, n, wpb, {}});
+      }
+}
+
 void add_full(std::vector<Benchmark>& out, const Options& o, const std::string& base, int op,
               int max_mult) {
   // BENCHMARK_TEMPLATE(name, SEGMENT_SIZE, WARPS_PER_BLOCK)->ARGS(): the template
@@ -132,30 +148,52 @@ void add_full(std::vector<Benchmark>& out, const Options& o, const std::string& 
 
 std::vector<Benchmark> registry(const Options& o) {
   std::vector<Benchmark> b;
-  // src/reduction/seg_wmma_16n.cu:215-221, seg_wmma_256n.cu:223-229, seg_wmma_256n_block.cu
-  add_segmented(b, o, "CUDA_WMMA_SEGMENTED_REDUCTION_16N", TCU_OP_SEGMENTED_REDUCE,
-                {16, 32, 64, 128, 256, 512, 1024});
-  add_segmented(b, o, "CUDA_WMMA_SEGMENTED_REDUCTION_256N", TCU_OP_SEGMENTED_REDUCE,
-                {256, 512, 1024, 2048, 4096, 8192, 16384});
-  add_segmented(b, o, "CUDA_WMMA_SEGMENTED_REDUCTION_256N_BLOCK", TCU_OP_SEGMENTED_REDUCE,
-                {256, 512, 1024, 2048, 4096, 8192, 16384});
-  add_tune(b, "CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_16N", TCU_OP_SEGMENTED_REDUCE, 16, 30);
-  add_tune(b, "CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_256N", TCU_OP_SEGMENTED_REDUCE, 256, 22);
-  add_tune(b, "CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_256N", TCU_OP_SEGMENTED_REDUCE, 256, 30);
-  // src/reduction/wmma_2kers.cu:172-194, wmma_2kers_block.cu:183-198
+  const std::initializer_list<size_t> k16n  = {16, 32, 64, 128, 256, 512, 1024};
+  const std::initializer_list<size_t> k256n = {256, 512, 1024, 2048, 4096, 8192, 16384};
+  // Every variant name of the reference maps onto the one kernel family of this
+  // library (warps per block, segments per warp, _OPT / _BLOCK are tuning knobs of
+  // kernels that no longer exist), so result files keep their names.
+  // src/reduction/seg_wmma_16n.cu:215-221, seg_wmma_16n_opt.cu:209-221, seg_wmma_16n_block.cu:213-235,
+  // seg_wmma_256n.cu:223-229, seg_wmma_256n_block.cu, seg_wmma_16.cu:132-147, seg_wmma_256.cu
+  for (const char* v : {"", "_OPT", "_BLOCK"}) {
+    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_REDUCTION_16N") + v, TCU_OP_SEGMENTED_REDUCE, k16n);
+    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_16N") + v, TCU_OP_SEGMENTED_REDUCE, 16, 30);
+  }
+  for (const char* v : {"", "_BLOCK"}) {
+    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, k256n);
+    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, 256, 22);
+    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, 256, 30);
+  }
+  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_REDUCTION_16", TCU_OP_SEGMENTED_REDUCE, 16);
+  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_REDUCTION_256", TCU_OP_SEGMENTED_REDUCE, 256);
+  // src/reduction/wmma_2kers.cu:172-194, wmma_2kers_block.cu:173-198, wmma_cg.cu:171-195,
+  // wmma_atomic.cu:163-185
   add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BASE_16", TCU_OP_FULL_REDUCE, 16);
   add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BASE_256", TCU_OP_FULL_REDUCE, 16);
+  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BLOCK_BASE_16", TCU_OP_FULL_REDUCE, 256);
   add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BLOCK_BASE_256", TCU_OP_FULL_REDUCE, 256);
-  // src/prefixsum/seg_wmma_16n.cu:217-223, seg_wmma_256n.cu:216-222
-  add_segmented(b, o, "CUDA_WMMA_SEGMENTED_PREFIXSUM_16N", TCU_OP_SEGMENTED_SCAN,
-                {16, 32, 64, 128, 256, 512, 1024});
-  add_segmented(b, o, "CUDA_WMMA_SEGMENTED_PREFIXSUM_256N", TCU_OP_SEGMENTED_SCAN,
-                {256, 512, 1024, 2048, 4096, 8192, 16384});
-  add_tune(b, "CUDA_WMMA_TUNE_SEGMENTED_PREFIXSUM_16N", TCU_OP_SEGMENTED_SCAN, 16, 30);
-  add_tune(b, "CUDA_WMMA_TUNE_SEGMENTED_PREFIXSUM_256N", TCU_OP_SEGMENTED_SCAN, 256, 30);
-  // src/prefixsum/wmma_3kers.cu:161-180, wmma_3kers_block.cu
+  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_CG", TCU_OP_FULL_REDUCE, 1024);
+  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_ATOMIC_W_ATOMIC_BALLOT", TCU_OP_FULL_REDUCE, 16);
+  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_ATOMIC_W_BLOCK_SYNC", TCU_OP_FULL_REDUCE, 16);
+  // src/prefixsum/seg_wmma_16n.cu:217-223, seg_wmma_16n_opt.cu:211-223, seg_wmma_16n_block.cu:216-238,
+  // seg_wmma_256n.cu:216-222, seg_wmma_256n_block.cu:211-233, seg_wmma_16.cu, seg_wmma_256.cu
+  for (const char* v : {"", "_OPT", "_BLOCK"}) {
+    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_PREFIXSUM_16N") + v, TCU_OP_SEGMENTED_SCAN, k16n);
+    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_PREFIXSUM_16N") + v, TCU_OP_SEGMENTED_SCAN, 16, 30);
+  }
+  for (const char* v : {"", "_BLOCK"}) {
+    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_PREFIXSUM_256N") + v, TCU_OP_SEGMENTED_SCAN, k256n);
+    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_PREFIXSUM_256N") + v, TCU_OP_SEGMENTED_SCAN, 256, 30);
+  }
+  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_PREFIXSUM_16", TCU_OP_SEGMENTED_SCAN, 16);
+  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_PREFIXSUM_256", TCU_OP_SEGMENTED_SCAN, 256);
+  // src/prefixsum/wmma_3kers.cu:161-183, wmma_3kers_block.cu:175-185, wmma_cg.cu:183-207,
+  // wmma_atomic.cu:176-200
   add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_3KERS", TCU_OP_FULL_SCAN, 16);
-  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_3KERS_BLOCK", TCU_OP_FULL_SCAN, 16);
+  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_3KERS_BLOCK", TCU_OP_FULL_SCAN, 256);
+  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_CG", TCU_OP_FULL_SCAN, 1024);
+  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_ATOMIC_W_ATOMIC_BALLOT", TCU_OP_FULL_SCAN, 1024);
+  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_ATOMIC_W_BLOCK_SYNC", TCU_OP_FULL_SCAN, 1024);
   return b;
 }
 
