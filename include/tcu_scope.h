@@ -32,7 +32,7 @@ extern "C" {
 typedef enum {
   TCU_OK              = 0,
   TCU_ERR_INVALID_ARG = 1, /* null / misaligned pointer, size overflow                  */
-  TCU_ERR_UNSUPPORTED = 2, /* segment size not a power of two >= 16, unknown algo/type  */
+  TCU_ERR_UNSUPPORTED = 2, /* segment size 0, unknown algo/type, algo without that size   */
   TCU_ERR_CUDA        = 3, /* a CUDA runtime call failed (see cudaGetLastError)         */
   TCU_ERR_TIMEOUT     = 4, /* a bounded device-side wait ran out (tcu_device_error)     */
   TCU_ERR_WORKSPACE   = 5, /* workspace missing or smaller than tcu_workspace_bytes()   */
@@ -71,8 +71,12 @@ typedef enum {
  * ..._256n (:301-356) and ..._256n_block (:418-485) and their drivers
  * CUDA_WMMA_SEGMENTED_REDUCTION_16N / _256N / _256N_BLOCK
  * (src/reduction/seg_wmma_16n.cu:137-221, seg_wmma_256n.cu:149-229).
- * segment_size: a power of two >= 16 (the sizes of the reference's dispatch
- * table, seg_wmma_16n.cu:146-172).  d_out: num_segments floats or halves.
+ * segment_size: any size >= 1.  Powers of two >= 16 (the sizes of the
+ * reference's dispatch table, seg_wmma_16n.cu:146-172, and of all its
+ * benchmarks) run the tiled kernels at HBM speed; the other multiples of 16
+ * the reference accepts, and every other size (tails masked), run a
+ * one-warp-per-segment kernel (TCU_ALGO_AUTO or TCU_ALGO_MMA only).
+ * d_out: num_segments floats or halves.
  * A workspace is needed only when segment_size > 16384.
  */
 int tcu_segmented_reduce_f16(const void* d_in, void* d_out, int out_type, size_t num_segments,

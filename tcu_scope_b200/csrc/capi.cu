@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "fill_kernels.cuh"
+#include "general_kernels.cuh"
 #include "reduce_kernels.cuh"
 #include "scan_kernels.cuh"
 #include "scan_lookback_kernel.cuh"
@@ -60,9 +61,10 @@ int sm_count() {
 }
 
 // log2 of a power-of-two segment size >= 16, folded into the kernel classes;
-// -1 for anything else.
+// kClassGeneral for every other size; -1 for zero.
 int segment_class(size_t s) {
-  if (s < 16 || (s & (s - 1)) != 0) return -1;
+  if (s == 0) return -1;
+  if (s < 16 || (s & (s - 1)) != 0) return kClassGeneral;
   int l = 0;
   while ((size_t(1) << l) < s) ++l;
   return l <= 14 ? l : kClassLong;
@@ -105,6 +107,31 @@ cudaError_t launch_pdl(void (*kernel)(Params), const Params& p, int grid, int th
   cfg.attrs    = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+// Same, for the kernels that take the segment size as a second argument.
+template <typename Params>
+cudaError_t launch_pdl(void (*kernel)(Params, unsigned long long), const Params& p,
+                       unsigned long long seg_elems, int grid, int threads, size_t smem,
+                       cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim          = dim3(grid);
+  cfg.blockDim         = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream           = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs    = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p, seg_elems);
+}
+
+// one warp per segment, eight warps per CTA, at most eight CTAs per SM
+int general_grid(size_t num_segments, int sms) {
+  const size_t ctas = (num_segments + kGeneralThreads / 32 - 1) / (kGeneralThreads / 32);
+  const size_t cap  = size_t(sms) * 8;
+  return int(ctas < cap ? ctas : cap);
 }
 
 template <int SC>
@@ -222,14 +249,15 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE &&
       algo != TCU_ALGO_TCGEN05)
     return TCU_ERR_UNSUPPORTED;
+  if (sc == kClassGeneral && algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA) return TCU_ERR_UNSUPPORTED;
   size_t n = 0;
   if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
   // the tcgen05 variant covers 16/32/64-element segments of arrays it can view as 64-wide rows
   if (algo == TCU_ALGO_TCGEN05 && (sc < 4 || sc > 6 || n % kSwizzleRowElems != 0))
     return TCU_ERR_UNSUPPORTED;
   if (n == 0) return TCU_OK;
-  // short classes store vectors of outputs, the long class single values
-  const uintptr_t out_mask = sc == kClassLong ? 3u : 15u;
+  // short classes store vectors of outputs, the long and the general class single values
+  const uintptr_t out_mask = sc >= kClassLong ? 3u : 15u;
   if (!d_in || !d_out || !aligned16(d_in) || (reinterpret_cast<uintptr_t>(d_out) & out_mask) != 0)
     return TCU_ERR_INVALID_ARG;
   if (d_out_f64 && (reinterpret_cast<uintptr_t>(d_out_f64) & 7u) != 0) return TCU_ERR_INVALID_ARG;
@@ -247,6 +275,13 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   int grid           = tiles < size_t(sms) ? int(tiles) : sms;
 
   cudaError_t e = cudaSuccess;
+  if (sc == kClassGeneral) {
+    e = launch_pdl(segment_size % 8 == 0 ? seg_reduce_general_kernel<true>
+                                         : seg_reduce_general_kernel<false>,
+                   p, (unsigned long long)segment_size, general_grid(num_segments, sms),
+                   kGeneralThreads, 0, st);
+    return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+  }
   if (algo == TCU_ALGO_TCGEN05) {
     CUtensorMap map;
     std::memset(&map, 0, sizeof(map));
@@ -294,6 +329,7 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
   if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE)
     return TCU_ERR_UNSUPPORTED;
+  if (sc == kClassGeneral && algo == TCU_ALGO_SHUFFLE) return TCU_ERR_UNSUPPORTED;
   size_t n = 0;
   if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
   if (n == 0) return TCU_OK;
@@ -314,6 +350,15 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   const bool f32     = out_type == TCU_OUT_F32;
 
   cudaError_t e = cudaSuccess;
+  if (sc == kClassGeneral) {
+    const int ggrid = general_grid(num_segments, sms);
+    const bool vec  = segment_size % 4 == 0;
+    void (*kernel)(ScanParams, unsigned long long) =
+        f32 ? (vec ? seg_scan_general_kernel<true, true> : seg_scan_general_kernel<true, false>)
+            : (vec ? seg_scan_general_kernel<false, true> : seg_scan_general_kernel<false, false>);
+    e = launch_pdl(kernel, p, (unsigned long long)segment_size, ggrid, kGeneralThreads, 0, st);
+    return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+  }
   if (sc == kClassLong) {
     const size_t need = scan_long_ws_bytes(n);
     if (!ws || ws_bytes < need || !aligned16(ws)) return TCU_ERR_WORKSPACE;
