@@ -133,6 +133,37 @@ int tcu_full_exclusive_scan_f16(const void* d_in, void* d_out, int out_type, siz
                                 void* d_workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * bfloat16 inputs.  Same operations, arguments, status codes, workspace sizes
+ * and segment sizes as the *_f16 entry points of the same name; d_in holds
+ * bfloat16 values and out_type TCU_OUT_F16 means "16-bit outputs in the type
+ * of the input", i.e. bfloat16.  No counterpart in the reference, which is
+ * fp16 only (half everywhere in src/reduction/kernel.cuh and
+ * src/prefixsum/kernel.cuh); the step next to it that mixed-precision callers
+ * need first.  Same kernels, compiled a second time with the bf16 form of the
+ * MMA, of the constant matrices and of the exact hi/lo split.  algo:
+ * TCU_ALGO_AUTO / _MMA / _SHUFFLE / _TCGEN05 as for fp16.
+ */
+int tcu_segmented_reduce_bf16(const void* d_in, void* d_out, int out_type, size_t num_segments,
+                              size_t segment_size, int algo, void* d_workspace,
+                              size_t workspace_bytes, void* stream);
+int tcu_segmented_scan_bf16(const void* d_in, void* d_out, int out_type, size_t num_segments,
+                            size_t segment_size, int algo, void* d_workspace,
+                            size_t workspace_bytes, void* stream);
+int tcu_segmented_exclusive_scan_bf16(const void* d_in, void* d_out, int out_type,
+                                      size_t num_segments, size_t segment_size, void* d_workspace,
+                                      size_t workspace_bytes, void* stream);
+int tcu_full_exclusive_scan_bf16(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                                 void* d_workspace, size_t workspace_bytes, void* stream);
+int tcu_full_reduce_bf16(const void* d_in, float* d_out, double* d_out_f64, size_t num_elements,
+                         int algo, void* d_workspace, size_t workspace_bytes, void* stream);
+int tcu_full_scan_bf16(const void* d_in, void* d_out, int out_type, size_t num_elements,
+                       const double* d_shard_totals, int shard_index, int algo,
+                       void* d_workspace, size_t workspace_bytes, void* stream);
+/* tcu_fill_f16 rounding the same values to bfloat16 instead. */
+int tcu_fill_bf16(void* d_out, size_t n, uint64_t seed, uint64_t first_index, int dist,
+                  void* stream);
+
+/*
  * tcu_full_scan_f16 for callers that must not allocate device memory.  It has
  * no counterpart in the reference, whose drivers cudaMalloc whatever they need.
  *

@@ -41,8 +41,10 @@ def _splitmix64(x: np.ndarray) -> np.ndarray:
         return x ^ (x >> np.uint64(31))
 
 
-def np_fill_f16(n: int, seed: int, first_index: int = 0, dist: str = "uniform_pm1") -> np.ndarray:
-    """uint16 bit patterns of the seeded input, element i = f(seed, first_index + i)."""
+def np_fill_f16(n: int, seed: int, first_index: int = 0, dist: str = "uniform_pm1",
+                fmt: str = "f16") -> np.ndarray:
+    """uint16 bit patterns of the seeded input, element i = f(seed, first_index + i), rounded
+    to fp16 or (fmt="bf16") to bfloat16."""
     key = _splitmix64(np.array([seed], dtype=np.uint64))[0]
     with np.errstate(over="ignore"):
         idx = (np.arange(n, dtype=np.uint64) + np.uint64(first_index) + key) & _M64
@@ -56,24 +58,36 @@ def np_fill_f16(n: int, seed: int, first_index: int = 0, dist: str = "uniform_pm
         v = ((u24 % 5) - 2).astype(np.float32)
     else:
         v = np.full(n, 0.001, dtype=np.float32)
+    if fmt == "bf16":
+        return f32_to_bf16_bits(v)
     return v.astype(np.float16).view(np.uint16)
 
 
-def _as_f64(in_u16: np.ndarray) -> np.ndarray:
-    return np.ascontiguousarray(in_u16, dtype=np.uint16).view(np.float16).astype(np.float64)
+def _as_f64(in_u16: np.ndarray, fmt: str = "f16") -> np.ndarray:
+    """float64 values of 16-bit patterns: fp16 (the reference's type) or bfloat16."""
+    u = np.ascontiguousarray(in_u16, dtype=np.uint16)
+    if fmt == "bf16":  # a bfloat16 is the upper half of a float32
+        return (u.astype(np.uint32) << np.uint32(16)).view(np.float32).astype(np.float64)
+    return u.view(np.float16).astype(np.float64)
 
 
-def np_segmented_reduce(in_u16: np.ndarray, segment_size: int) -> np.ndarray:
+def f32_to_bf16_bits(v: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even float32 -> bfloat16 bit patterns (finite inputs)."""
+    u = np.ascontiguousarray(v, dtype=np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def np_segmented_reduce(in_u16: np.ndarray, segment_size: int, fmt: str = "f16") -> np.ndarray:
     """Segment j = in[j*S:(j+1)*S] (src/reduction/seg_wmma_16n.cu:14-25); float64 sums."""
-    x = _as_f64(in_u16).reshape(-1, segment_size)
+    x = _as_f64(in_u16, fmt).reshape(-1, segment_size)
     return x.sum(axis=1, dtype=np.float64)
 
 
-def np_segmented_scan(in_u16: np.ndarray, segment_size: int) -> np.ndarray:
+def np_segmented_scan(in_u16: np.ndarray, segment_size: int, fmt: str = "f16") -> np.ndarray:
     """Inclusive running sum inside each segment (U[i][j]=1 for i<=j,
     src/prefixsum/kernel.cuh:60,79-81; the check the authors intended,
     src/prefixsum/wmma_3kers.cu:97-108)."""
-    x = _as_f64(in_u16).reshape(-1, segment_size)
+    x = _as_f64(in_u16, fmt).reshape(-1, segment_size)
     return np.cumsum(x, axis=1, dtype=np.float64).reshape(-1)
 
 
@@ -104,11 +118,16 @@ def np_check_f32(got: np.ndarray, ref: np.ndarray, rel: float = 1e-3, abs_floor:
     return int(bad.sum()), float(np.nanmax(err)) if err.size else 0.0, max_rel
 
 
-def np_check_f16(got_bits: np.ndarray, ref: np.ndarray, max_ulp: int = 2):
-    """Returns (violations, worst): distance in representable halves from half(ref)."""
-    ref_bits = ref.astype(np.float16).view(np.uint16)
+def np_check_f16(got_bits: np.ndarray, ref: np.ndarray, max_ulp: int = 2, fmt: str = "f16"):
+    """Returns (violations, worst): distance in representable halves (bfloat16s) from the
+    correctly rounded reference."""
     g = np.ascontiguousarray(got_bits, dtype=np.uint16)
-    nan = ((g & 0x7C00) == 0x7C00) & ((g & 0x3FF) != 0)
+    if fmt == "bf16":
+        ref_bits = f32_to_bf16_bits(ref.astype(np.float32))
+        nan = ((g & 0x7F80) == 0x7F80) & ((g & 0x7F) != 0)
+    else:
+        ref_bits = ref.astype(np.float16).view(np.uint16)
+        nan = ((g & 0x7C00) == 0x7C00) & ((g & 0x3FF) != 0)
     d = np.abs(half_order_key(g) - half_order_key(ref_bits))
     bad = nan | (d > max_ulp)
     return int(bad.sum()), int(d[~nan].max()) if (~nan).any() else 0

@@ -29,6 +29,20 @@ SIGNATURES = {
                                                  c_void_p, c_size_t, c_void_p]),
     "tcu_full_exclusive_scan_f16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p,
                                             c_size_t, c_void_p]),
+    "tcu_segmented_reduce_bf16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int,
+                                          c_void_p, c_size_t, c_void_p]),
+    "tcu_segmented_scan_bf16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_int,
+                                        c_void_p, c_size_t, c_void_p]),
+    "tcu_segmented_exclusive_scan_bf16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_size_t,
+                                                  c_void_p, c_size_t, c_void_p]),
+    "tcu_full_exclusive_scan_bf16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p,
+                                             c_size_t, c_void_p]),
+    "tcu_full_reduce_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p,
+                                     c_size_t, c_void_p]),
+    "tcu_full_scan_bf16": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int, c_int,
+                                   c_void_p, c_size_t, c_void_p]),
+    "tcu_fill_bf16": (c_int, [c_void_p, c_size_t, ctypes.c_uint64, ctypes.c_uint64, c_int,
+                              c_void_p]),
     "tcu_full_scan_f16_static": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int,
                                          c_int, c_void_p]),
     "tcu_workspace_bytes": (c_size_t, [c_int, c_size_t, c_size_t]),

@@ -45,11 +45,13 @@ def _sources() -> list[str]:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Compile csrc/capi.cu (which includes every kernel) into libtcu_scope.so."""
+    """Compile csrc/capi.cu (which includes every kernel; fp16 inputs) and csrc/capi_bf16.cu (the
+    same sources for bf16 inputs) into libtcu_scope.so."""
     srcs = _sources()
     if not force and _newer_than(LIB_PATH, srcs):
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", LIB_PATH, os.path.join(CSRC, "capi.cu")]
+    cmd = [_nvcc(), *NVCC_FLAGS, "--threads", "2", "-shared", "-o", LIB_PATH,
+           os.path.join(CSRC, "capi.cu"), os.path.join(CSRC, "capi_bf16.cu")]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -19,9 +19,22 @@
 #include "shuffle_kernels.cuh"
 #include "tcgen05_reduce_kernel.cuh"
 
+#if TCU_BF16
+// Second compilation of this file (capi_bf16.cu): the same entry points for
+// bf16 inputs, under their _bf16 names; 16-bit outputs are bf16 as well.  The
+// entry points that are not about an element type exist once, in the fp16 build.
+#define tcu_segmented_reduce_f16 tcu_segmented_reduce_bf16
+#define tcu_segmented_scan_f16 tcu_segmented_scan_bf16
+#define tcu_segmented_exclusive_scan_f16 tcu_segmented_exclusive_scan_bf16
+#define tcu_full_exclusive_scan_f16 tcu_full_exclusive_scan_bf16
+#define tcu_full_reduce_f16 tcu_full_reduce_bf16
+#define tcu_full_scan_f16 tcu_full_scan_bf16
+#define tcu_fill_f16 tcu_fill_bf16
+#endif
+
 namespace {
 
-using namespace tcu;
+using namespace TCU_NS;
 
 constexpr int kMaxDevices    = 64;
 constexpr size_t kWsHeader   = 256;   // counters live in the first 256 bytes
@@ -36,12 +49,14 @@ int g_sm_count[kMaxDevices];
 // lives in every GPU's memory from the moment the library is loaded there.
 // In host code the name below is only a handle for the runtime, never a device
 // address: the address is looked up once per device with cudaGetSymbolAddress.
+#if !TCU_BF16
 constexpr size_t kStaticScanMaxElems = size_t(1) << 30;
 constexpr size_t kStaticScanMaxTiles = kStaticScanMaxElems / kTileElems;
 constexpr size_t kStaticScratchBytes =
     kWsHeader + kStaticScanMaxTiles * 8 + (kStaticScanMaxTiles / 32 + kStaticScanMaxTiles / 2 + 2) * 8;
 static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScratchBytes];
 void* g_static_scan_scratch_addr[kMaxDevices];  // device address, per device; null = not looked up
+#endif
 
 int current_device() {
   int dev = 0;
@@ -462,6 +477,7 @@ int tcu_full_scan_f16(const void* d_in, void* d_out, int out_type, size_t num_el
                    static_cast<cudaStream_t>(stream));
 }
 
+#if !TCU_BF16
 int tcu_full_scan_f16_static(const void* d_in, void* d_out, int out_type, size_t num_elements,
                              const double* d_shard_totals, int shard_index, int algo,
                              void* stream) {
@@ -496,6 +512,8 @@ size_t tcu_workspace_bytes(int op, size_t num_elements, size_t segment_size) {
   }
 }
 
+#endif  // !TCU_BF16
+
 int tcu_fill_f16(void* d_out, size_t n, uint64_t seed, uint64_t first_index, int dist,
                  void* stream) {
   if (n == 0) return TCU_OK;
@@ -511,7 +529,17 @@ int tcu_fill_f16(void* d_out, size_t n, uint64_t seed, uint64_t first_index, int
   return cudaGetLastError() == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
 }
 
-int tcu_device_error(unsigned int* bits, int clear) {
+// Each of the two builds has its own device error word; this reads (and clears)
+// the one of the build it is compiled in.  Not part of the public header.
+#if TCU_BF16
+#define tcu_error_word_of_this_build tcu_error_word_bf16_build
+#else
+#define tcu_error_word_of_this_build tcu_error_word_f16_build
+#endif
+int tcu_error_word_f16_build(unsigned int* bits, int clear);
+int tcu_error_word_bf16_build(unsigned int* bits, int clear);
+
+int tcu_error_word_of_this_build(unsigned int* bits, int clear) {
   unsigned int v = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return TCU_ERR_CUDA;
   if (cudaMemcpyFromSymbol(&v, g_error_word, sizeof(v)) != cudaSuccess) return TCU_ERR_CUDA;
@@ -519,8 +547,17 @@ int tcu_device_error(unsigned int* bits, int clear) {
     const unsigned int z = 0;
     if (cudaMemcpyToSymbol(g_error_word, &z, sizeof(z)) != cudaSuccess) return TCU_ERR_CUDA;
   }
-  if (bits) *bits = v;
-  return v ? TCU_ERR_TIMEOUT : TCU_OK;
+  *bits = v;
+  return TCU_OK;
+}
+
+#if !TCU_BF16
+int tcu_device_error(unsigned int* bits, int clear) {
+  unsigned int a = 0, b = 0;
+  if (tcu_error_word_f16_build(&a, clear) != TCU_OK) return TCU_ERR_CUDA;
+  if (tcu_error_word_bf16_build(&b, clear) != TCU_OK) return TCU_ERR_CUDA;
+  if (bits) *bits = a | b;
+  return (a | b) ? TCU_ERR_TIMEOUT : TCU_OK;
 }
 
 #ifdef TCU_LB_PROFILE
@@ -553,6 +590,10 @@ const char* tcu_status_string(int status) {
   }
 }
 
+#endif  // !TCU_BF16
+
 }  // extern "C"
 
+#if !TCU_BF16
 #include "host_pipeline.inl"
+#endif

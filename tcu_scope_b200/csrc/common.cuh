@@ -4,11 +4,30 @@
 #pragma once
 
 #include <cuda.h>  // CUtensorMap (the type only; the encoder is looked up at run time)
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-namespace tcu {
+// The library is compiled twice from the same sources: once for fp16 inputs
+// (TCU_BF16 = 0, namespace tcu) and once for bf16 inputs (TCU_BF16 = 1,
+// namespace tcu_bf16).  Everything that depends on the 16-bit element type is
+// in the few helpers below: the MMA instruction, the constant 1.0, the exact
+// hi/lo split and the conversions of the 16-bit outputs.
+#ifndef TCU_BF16
+#define TCU_BF16 0
+#endif
+#if TCU_BF16
+#define TCU_NS tcu_bf16
+#define TCU_MMA_TYPES "f32.bf16.bf16.f32"
+#define TCU_X2 "bf16x2"
+#else
+#define TCU_NS tcu
+#define TCU_MMA_TYPES "f32.f16.f16.f32"
+#define TCU_X2 "f16x2"
+#endif
+
+namespace TCU_NS {
 
 // ---------------------------------------------------------------- geometry
 // One CTA tile is what a single TMA bulk copy brings into one ring stage.  A
@@ -219,7 +238,7 @@ __device__ __forceinline__ Acc mma16816(uint32_t a0, uint32_t a1, uint32_t a2, u
                                         uint32_t b0, uint32_t b1, Acc c) {
   Acc d;
   asm(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "mma.sync.aligned.m16n8k16.row.col." TCU_MMA_TYPES " "
       "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=f"(d.d0), "=f"(d.d1), "=f"(d.d2), "=f"(d.d3)
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c.d0), "f"(c.d1), "f"(c.d2),
@@ -227,7 +246,33 @@ __device__ __forceinline__ Acc mma16816(uint32_t a0, uint32_t a1, uint32_t a2, u
   return d;
 }
 
-constexpr uint32_t kOnesH2 = 0x3C003C00u;  // half2(1, 1)
+constexpr uint32_t kOne16  = TCU_BF16 ? 0x3F80u : 0x3C00u;  // 1.0 in the element type
+constexpr uint32_t kOnesH2 = kOne16 | (kOne16 << 16);       // (1, 1)
+
+// Conversions of 16-bit outputs and (for the CUDA-core ablation) inputs.
+__device__ __forceinline__ uint32_t pack2_rn(float a, float b) {
+#if TCU_BF16
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+#else
+  const __half2 v = __floats2half2_rn(a, b);
+#endif
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint16_t to16_rn(float a) {
+#if TCU_BF16
+  const __nv_bfloat16 v = __float2bfloat16_rn(a);
+#else
+  const __half v = __float2half_rn(a);
+#endif
+  return *reinterpret_cast<const uint16_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+#if TCU_BF16
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+#else
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+#endif
+}
 
 // x = hi + lo exactly, for every finite half x.  hi is x rounded to a multiple
 // of 2^-13 or coarser (the ulp of half in [0.25, 0.5) after adding 0.375), so
@@ -236,11 +281,11 @@ constexpr uint32_t kOnesH2 = 0x3C003C00u;  // half2(1, 1)
 // the two parts to separate tensor-core accumulators makes every partial sum
 // exact, whatever order and rounding the hardware adder uses.
 __device__ __forceinline__ void split_hi_lo(uint32_t x, uint32_t& hi, uint32_t& lo) {
-  constexpr uint32_t kMagic = 0x36003600u;  // half2(0.375, 0.375)
+  constexpr uint32_t kMagic = TCU_BF16 ? 0x3EC03EC0u : 0x36003600u;  // (0.375, 0.375)
   uint32_t t;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(t) : "r"(x), "r"(kMagic));
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(t), "r"(kMagic));
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(x), "r"(hi));
+  asm("add.rn." TCU_X2 " %0, %1, %2;" : "=r"(t) : "r"(x), "r"(kMagic));
+  asm("sub.rn." TCU_X2 " %0, %1, %2;" : "=r"(hi) : "r"(t), "r"(kMagic));
+  asm("sub.rn." TCU_X2 " %0, %1, %2;" : "=r"(lo) : "r"(x), "r"(hi));
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

@@ -6,7 +6,7 @@
 
 #include "common.cuh"
 
-namespace tcu {
+namespace TCU_NS {
 
 __host__ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
   x += 0x9E3779B97F4A7C15ull;
@@ -37,12 +37,10 @@ __global__ void fill_f16_kernel(uint4* out, size_t groups, uint64_t seed, uint64
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const uint64_t i0 = key + first_index + grp * 8 + 2 * e;
-      const __half2 h2 = __floats2half2_rn(dist_value(splitmix64(i0), dist),
-                                           dist_value(splitmix64(i0 + 1), dist));
-      w[e] = *reinterpret_cast<const uint32_t*>(&h2);
+      w[e] = pack2_rn(dist_value(splitmix64(i0), dist), dist_value(splitmix64(i0 + 1), dist));
     }
     out[grp] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

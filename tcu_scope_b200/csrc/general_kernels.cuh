@@ -18,7 +18,7 @@
 #include "reduce_kernels.cuh"
 #include "scan_kernels.cuh"
 
-namespace tcu {
+namespace TCU_NS {
 
 constexpr int kClassGeneral   = 16;  // any segment size that is not a power of two >= 16
 constexpr int kGeneralThreads = 256;
@@ -179,4 +179,4 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
   }
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

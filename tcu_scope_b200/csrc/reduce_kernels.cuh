@@ -19,7 +19,7 @@
 
 #include "common.cuh"
 
-namespace tcu {
+namespace TCU_NS {
 
 struct ReduceParams {
   const uint8_t* in;                     // fp16 input, 16-byte aligned
@@ -44,7 +44,7 @@ __device__ __forceinline__ void store_seg(void* out, bool f32, unsigned long lon
   if (f32)
     static_cast<float*>(out)[idx] = v;
   else
-    static_cast<__half*>(out)[idx] = __float2half_rn(v);
+    static_cast<uint16_t*>(out)[idx] = to16_rn(v);
 }
 
 // ---------------------------------------------------------------------------
@@ -113,10 +113,8 @@ __device__ __forceinline__ float2 reduce_slice(const uint8_t* slice, void* out, 
         *reinterpret_cast<float4*>(static_cast<float*>(out) + seg_base + s0) =
             make_float4(o0, o1, o2, o3);
       } else {
-        const __half2 a = __floats2half2_rn(o0, o1), b = __floats2half2_rn(o2, o3);
-        *reinterpret_cast<uint2*>(static_cast<__half*>(out) + seg_base + s0) =
-            make_uint2(*reinterpret_cast<const uint32_t*>(&a),
-                       *reinterpret_cast<const uint32_t*>(&b));
+        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(out) + seg_base + s0) =
+            make_uint2(pack2_rn(o0, o1), pack2_rn(o2, o3));
       }
     } else {
       const float o[4] = {o0, o1, o2, o3};
@@ -159,10 +157,7 @@ __device__ __forceinline__ float2 reduce_slice(const uint8_t* slice, void* out, 
 // are fp32 adds and warp shuffles instead of MMAs.  Exists so that a profile
 // can show what the tensor-core formulation buys; not used by default.
 __device__ __forceinline__ float sum8_halves(const uint4& w) {
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-  const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
-  const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
+  const float2 a = unpack2(w.x), b = unpack2(w.y), c = unpack2(w.z), d = unpack2(w.w);
   return ((a.x + a.y) + (b.x + b.y)) + ((c.x + c.y) + (d.x + d.y));
 }
 
@@ -462,4 +457,4 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
   }
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

@@ -22,7 +22,7 @@
 
 #include "common.cuh"
 
-namespace tcu {
+namespace TCU_NS {
 
 struct ScanParams {
   const uint8_t* in;             // fp16 input, 16-byte aligned
@@ -54,7 +54,7 @@ __device__ __forceinline__ ScanOperands make_scan_operands(int lane, bool exclus
   const int g = lane >> 2, t = lane & 3;
   const int qa = 4 * (g >> 1) + (g & 1) - (exclusive ? 1 : 0), qb = qa + 2;
   auto pack = [](bool e0, bool e1) -> uint32_t {
-    return (e0 ? 0x3C00u : 0u) | (e1 ? 0x3C000000u : 0u);
+    return (e0 ? kOne16 : 0u) | (e1 ? (kOne16 << 16) : 0u);
   };
   ScanOperands o;
   o.ua0 = pack(4 * t + 0 <= qa, 4 * t + 1 <= qa);
@@ -77,9 +77,8 @@ __device__ __forceinline__ void store4(void* out, unsigned long long idx, float 
     else
       *reinterpret_cast<float4*>(dst) = make_float4(r0, r1, r2, r3);
   } else {
-    const __half2 a = __floats2half2_rn(r0, r1), b = __floats2half2_rn(r2, r3);
-    const uint32_t ua = *reinterpret_cast<const uint32_t*>(&a), ub = *reinterpret_cast<const uint32_t*>(&b);
-    __half* dst = static_cast<__half*>(out) + idx;
+    const uint32_t ua = pack2_rn(r0, r1), ub = pack2_rn(r2, r3);
+    uint16_t* dst = static_cast<uint16_t*>(out) + idx;
     if constexpr (kStream)
       asm volatile("st.global.cs.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(ua), "r"(ub) : "memory");
     else
@@ -472,4 +471,4 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
   }
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

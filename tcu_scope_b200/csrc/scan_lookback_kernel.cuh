@@ -31,7 +31,7 @@
 
 #include "scan_kernels.cuh"
 
-namespace tcu {
+namespace TCU_NS {
 
 #ifndef TCU_LB_STREAM_STORES
 #define TCU_LB_STREAM_STORES 1
@@ -499,4 +499,4 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   }
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

@@ -7,7 +7,7 @@
 
 #include "scan_kernels.cuh"
 
-namespace tcu {
+namespace TCU_NS {
 
 template <int SC, bool OUT32>
 __global__ void __launch_bounds__(kThreads, 1) shuffle_scan_kernel(const ScanParams p) {
@@ -89,10 +89,7 @@ __global__ void __launch_bounds__(kThreads, 1) shuffle_scan_kernel(const ScanPar
         const uint4 w = lds128(slice + 512 * j + 16 * lane);
         float f[8];
         {
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-          const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-          const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
-          const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
+          const float2 a = unpack2(w.x), b = unpack2(w.y), c = unpack2(w.z), d = unpack2(w.w);
           f[0] = a.x; f[1] = f[0] + a.y; f[2] = f[1] + b.x; f[3] = f[2] + b.y;
           f[4] = f[3] + c.x; f[5] = f[4] + c.y; f[6] = f[5] + d.x; f[7] = f[6] + d.y;
         }
@@ -124,4 +121,4 @@ __global__ void __launch_bounds__(kThreads, 1) shuffle_scan_kernel(const ScanPar
   }
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

@@ -20,7 +20,7 @@
 #include "common.cuh"
 #include "reduce_kernels.cuh"
 
-namespace tcu {
+namespace TCU_NS {
 
 constexpr int kUmmaRows       = 128;                               // rows (TMEM lanes) per tile
 constexpr int kUmmaTileElems  = kUmmaRows * kSwizzleRowElems;      // 8192 halves
@@ -52,9 +52,12 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
          (1ull << 46) | (2ull << 61);
 }
 
-// 32-bit instruction descriptor: fp32 accumulator, f16 x f16, both K-major,
-// N = 16 (field N >> 3), M = 128 (field M >> 4).
-constexpr uint32_t kUmmaInstrDesc = (1u << 4) | ((kUmmaN >> 3) << 17) | ((kUmmaRows >> 4) << 24);
+// 32-bit instruction descriptor: fp32 accumulator (bit 4), A and B formats
+// (bits 7-9 and 10-12: 0 = f16, 1 = bf16), both K-major, N = 16 (field
+// N >> 3), M = 128 (field M >> 4).
+constexpr uint32_t kUmmaAB        = TCU_BF16 ? 1u : 0u;
+constexpr uint32_t kUmmaInstrDesc = (1u << 4) | (kUmmaAB << 7) | (kUmmaAB << 10) |
+                                    ((kUmmaN >> 3) << 17) | ((kUmmaRows >> 4) << 24);
 
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                          uint32_t accumulate) {
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   for (int idx = threadIdx.x; idx < kUmmaN * kSwizzleRowElems; idx += kUmmaThreads) {
     const int n = idx / kSwizzleRowElems, k = idx % kSwizzleRowElems;
     const bool one = n < kSegsPerRow && (k >> LOG2S) == n;
-    *reinterpret_cast<uint16_t*>(bmat + swizzle128(n * 128 + k * 2)) = one ? 0x3C00u : 0u;
+    *reinterpret_cast<uint16_t*>(bmat + swizzle128(n * 128 + k * 2)) = one ? static_cast<uint16_t>(kOne16) : uint16_t(0);
   }
   // make the generic-proxy writes of B visible to the tensor core's async reads
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -188,10 +191,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           if (out_f32) {
             *reinterpret_cast<float4*>(static_cast<float*>(p.out) + seg) = make_float4(v0, v1, v2, v3);
           } else {
-            const __half2 h0 = __floats2half2_rn(v0, v1), h1 = __floats2half2_rn(v2, v3);
-            *reinterpret_cast<uint2*>(static_cast<__half*>(p.out) + seg) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&h0),
-                           *reinterpret_cast<const uint32_t*>(&h1));
+            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + seg) =
+                make_uint2(pack2_rn(v0, v1), pack2_rn(v2, v3));
           }
         } else if constexpr (kSegsPerRow == 2) {
           store_seg(p.out, out_f32, seg, v0);
@@ -214,4 +215,4 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   }
 }
 
-}  // namespace tcu
+}  // namespace TCU_NS

@@ -37,19 +37,26 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _out_code(dtype: torch.dtype) -> int:
-    if dtype == torch.float16:
-        return OUT_F16
+def _out_code(dtype: torch.dtype, in_dtype: torch.dtype = torch.float16) -> int:
+    """16-bit outputs have the type of the input (float16 or bfloat16)."""
     if dtype == torch.float32:
         return OUT_F32
-    raise TypeError(f"output dtype must be float16 or float32, got {dtype}")
+    if dtype == in_dtype and dtype in (torch.float16, torch.bfloat16):
+        return OUT_F16
+    raise TypeError(f"output dtype must be float32 or the input's {in_dtype}, got {dtype}")
 
 
-def _require_input(x: torch.Tensor) -> None:
+def _require_input(x: torch.Tensor) -> str:
+    """Checks the input and returns the suffix of the entry points for its type."""
     if not x.is_cuda:
         raise RuntimeError("input must be a CUDA tensor: there is no CPU path in this library")
-    if x.dtype != torch.float16 or not x.is_contiguous():
-        raise TypeError("input must be a contiguous float16 tensor")
+    if x.dtype not in (torch.float16, torch.bfloat16) or not x.is_contiguous():
+        raise TypeError("input must be a contiguous float16 or bfloat16 tensor")
+    return "f16" if x.dtype == torch.float16 else "bf16"
+
+
+def _default_out(out_dtype: torch.dtype, x: torch.Tensor) -> torch.dtype:
+    return x.dtype if out_dtype in (torch.float16, torch.bfloat16) else out_dtype
 
 
 def workspace_bytes(op: int, num_elements: int, segment_size: int) -> int:
@@ -66,27 +73,28 @@ def _workspace(op: int, n: int, segment_size: int, device, workspace):
 
 
 def fill(out: torch.Tensor, seed: int, first_index: int = 0, dist: str = "uniform_pm1") -> torch.Tensor:
-    """Fill a float16 CUDA tensor with element i = f(seed, first_index + i)."""
-    _require_input(out)
-    _check(_lib.load().tcu_fill_f16(out.data_ptr(), out.numel(), seed, first_index, DIST[dist],
-                                    _stream()), "tcu_fill_f16")
+    """Fill a float16 or bfloat16 CUDA tensor with element i = f(seed, first_index + i)."""
+    t = _require_input(out)
+    fn = getattr(_lib.load(), f"tcu_fill_{t}")
+    _check(fn(out.data_ptr(), out.numel(), seed, first_index, DIST[dist], _stream()),
+           f"tcu_fill_{t}")
     return out
 
 
 def segmented_reduce(x: torch.Tensor, segment_size: int, out_dtype=torch.float32, algo="auto",
                      out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
     """out[j] = sum(x[j*segment_size:(j+1)*segment_size])."""
-    _require_input(x)
+    t = _require_input(x)
     n = x.numel()
     if segment_size <= 0 or n % segment_size:
         raise ValueError("num_elements must be a multiple of segment_size")
     segs = n // segment_size
     if out is None:
-        out = torch.empty(segs, dtype=out_dtype, device=x.device)
+        out = torch.empty(segs, dtype=_default_out(out_dtype, x), device=x.device)
     ws, ws_ptr, ws_bytes = _workspace(OP_SEGMENTED_REDUCE, n, segment_size, x.device, workspace)
-    _check(_lib.load().tcu_segmented_reduce_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype),
-                                                segs, segment_size, ALGO[algo], ws_ptr, ws_bytes,
-                                                _stream()), "tcu_segmented_reduce_f16")
+    fn = getattr(_lib.load(), f"tcu_segmented_reduce_{t}")
+    _check(fn(x.data_ptr(), out.data_ptr(), _out_code(out.dtype, x.dtype), segs, segment_size,
+              ALGO[algo], ws_ptr, ws_bytes, _stream()), f"tcu_segmented_reduce_{t}")
     return out
 
 
@@ -94,37 +102,38 @@ def segmented_scan(x: torch.Tensor, segment_size: int, out_dtype=torch.float16, 
                    out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
                    exclusive: bool = False):
     """Prefix sum inside every segment of segment_size elements (inclusive unless ``exclusive``)."""
-    _require_input(x)
+    t = _require_input(x)
     n = x.numel()
     if segment_size <= 0 or n % segment_size:
         raise ValueError("num_elements must be a multiple of segment_size")
     if out is None:
-        out = torch.empty(n, dtype=out_dtype, device=x.device)
+        out = torch.empty(n, dtype=_default_out(out_dtype, x), device=x.device)
     ws, ws_ptr, ws_bytes = _workspace(OP_SEGMENTED_SCAN, n, segment_size, x.device, workspace)
+    code = _out_code(out.dtype, x.dtype)
     if exclusive:
-        _check(_lib.load().tcu_segmented_exclusive_scan_f16(
-            x.data_ptr(), out.data_ptr(), _out_code(out.dtype), n // segment_size, segment_size,
-            ws_ptr, ws_bytes, _stream()), "tcu_segmented_exclusive_scan_f16")
+        fn = getattr(_lib.load(), f"tcu_segmented_exclusive_scan_{t}")
+        _check(fn(x.data_ptr(), out.data_ptr(), code, n // segment_size, segment_size, ws_ptr,
+                  ws_bytes, _stream()), f"tcu_segmented_exclusive_scan_{t}")
         return out
-    _check(_lib.load().tcu_segmented_scan_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype),
-                                              n // segment_size, segment_size, ALGO[algo], ws_ptr,
-                                              ws_bytes, _stream()), "tcu_segmented_scan_f16")
+    fn = getattr(_lib.load(), f"tcu_segmented_scan_{t}")
+    _check(fn(x.data_ptr(), out.data_ptr(), code, n // segment_size, segment_size, ALGO[algo],
+              ws_ptr, ws_bytes, _stream()), f"tcu_segmented_scan_{t}")
     return out
 
 
 def full_reduce(x: torch.Tensor, algo="auto", workspace: torch.Tensor | None = None,
                 out: torch.Tensor | None = None, out_f64: torch.Tensor | None = None):
     """Sum of all elements; returns (float32[1], float64[1]) device tensors."""
-    _require_input(x)
+    t = _require_input(x)
     n = x.numel()
     if out is None:
         out = torch.empty(1, dtype=torch.float32, device=x.device)
     if out_f64 is None:
         out_f64 = torch.empty(1, dtype=torch.float64, device=x.device)
     ws, ws_ptr, ws_bytes = _workspace(OP_FULL_REDUCE, n, n, x.device, workspace)
-    _check(_lib.load().tcu_full_reduce_f16(x.data_ptr(), out.data_ptr(), out_f64.data_ptr(), n,
-                                           ALGO[algo], ws_ptr, ws_bytes, _stream()),
-           "tcu_full_reduce_f16")
+    fn = getattr(_lib.load(), f"tcu_full_reduce_{t}")
+    _check(fn(x.data_ptr(), out.data_ptr(), out_f64.data_ptr(), n, ALGO[algo], ws_ptr, ws_bytes,
+              _stream()), f"tcu_full_reduce_{t}")
     return out, out_f64
 
 
@@ -133,24 +142,24 @@ def full_scan(x: torch.Tensor, out_dtype=torch.float32, algo="auto",
               out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
               exclusive: bool = False):
     """Inclusive prefix sum over the whole tensor (seeded by earlier shards' totals)."""
-    _require_input(x)
+    t = _require_input(x)
     n = x.numel()
     if out is None:
-        out = torch.empty(n, dtype=out_dtype, device=x.device)
+        out = torch.empty(n, dtype=_default_out(out_dtype, x), device=x.device)
     if shard_totals is not None and shard_totals.dtype != torch.float64:
         raise TypeError("shard_totals must be float64")
     ws, ws_ptr, ws_bytes = _workspace(OP_FULL_SCAN, n, n, x.device, workspace)
     if exclusive:
         if shard_totals is not None:
             raise ValueError("the exclusive full scan has no multi-GPU seed")
-        _check(_lib.load().tcu_full_exclusive_scan_f16(x.data_ptr(), out.data_ptr(),
-                                                       _out_code(out.dtype), n, ws_ptr, ws_bytes,
-                                                       _stream()), "tcu_full_exclusive_scan_f16")
+        fn = getattr(_lib.load(), f"tcu_full_exclusive_scan_{t}")
+        _check(fn(x.data_ptr(), out.data_ptr(), _out_code(out.dtype, x.dtype), n, ws_ptr, ws_bytes,
+                  _stream()), f"tcu_full_exclusive_scan_{t}")
         return out
     st_ptr = shard_totals.data_ptr() if shard_totals is not None else None
-    _check(_lib.load().tcu_full_scan_f16(x.data_ptr(), out.data_ptr(), _out_code(out.dtype), n,
-                                         st_ptr, shard_index, ALGO[algo], ws_ptr, ws_bytes,
-                                         _stream()), "tcu_full_scan_f16")
+    fn = getattr(_lib.load(), f"tcu_full_scan_{t}")
+    _check(fn(x.data_ptr(), out.data_ptr(), _out_code(out.dtype, x.dtype), n, st_ptr, shard_index,
+              ALGO[algo], ws_ptr, ws_bytes, _stream()), f"tcu_full_scan_{t}")
     return out
 
 

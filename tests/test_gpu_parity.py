@@ -256,12 +256,12 @@ def test_error_behaviour(tcu):
     with pytest.raises(ValueError):
         tcu.segmented_reduce(x, 48)  # 4096 is not a multiple of 48
     with pytest.raises(tcu.TcuError) as e:
-        tcu.segmented_reduce(x[:4032], 48)  # a multiple, but not a power of two
-    # a segment size that is not a power of two is rejected like the
-    # reference's "invalid segment size" (src/reduction/seg_wmma_16n.cu:172)
+        tcu.segmented_reduce(x[:4032], 48, algo="shuffle")  # the ablation: powers of two only
+    # a segment size of zero is rejected like the reference's "invalid segment
+    # size" (src/reduction/seg_wmma_16n.cu:172)
     lib = tcu._lib.load()
     out = torch.empty(4096, dtype=torch.float32, device="cuda")
-    assert lib.tcu_segmented_reduce_f16(x.data_ptr(), out.data_ptr(), 1, 4096 // 48, 48, 0, None, 0, None) == 2
+    assert lib.tcu_segmented_reduce_f16(x.data_ptr(), out.data_ptr(), 1, 4, 0, 0, None, 0, None) == 2
     assert lib.tcu_segmented_reduce_f16(x.data_ptr() + 2, out.data_ptr(), 1, 16, 16, 0, None, 0, None) == 1
     # long segments without a workspace
     big = device_input(tcu, 1 << 16, 2)
