@@ -155,7 +155,10 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
       // the segment so far, as an exact multiple of 2^-13 plus a small rest
       const double carry_hi = rint(carry * 8192.0) * (1.0 / 8192.0);
       const float xh = (float)carry_hi, xl = (float)(carry - (double)xh);
-      const Acc c_h{ch_lo + xh, ch_lo + xh, ch_hi + xh, ch_hi + xh};
+      // a large xh is held back and added last (see scan_step_independent)
+      const bool fold = fabsf(xh) < 1024.f;
+      const float xf = fold ? xh : 0.f, big = fold ? 0.f : xh;
+      const Acc c_h{ch_lo + xf, ch_lo + xf, ch_hi + xf, ch_hi + xf};
       const Acc c_l{cl_lo + xl, cl_lo + xl, cl_hi + xl, cl_hi + xl};
       const Acc ha = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ua0, ops.ua1, c_h);
       const Acc hb = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ub0, ops.ub1, c_h);
@@ -164,15 +167,15 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
       const unsigned long long out_lo = seg_base + e0 + off_lo / 2;
       if constexpr (kVec) {
         if (n_lo > 0)
-          store4<OUT32>(p.out, out_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0, hb.d1 + lb.d1);
+          store4<OUT32>(p.out, out_lo, (ha.d0 + la.d0) + big, (ha.d1 + la.d1) + big, (hb.d0 + lb.d0) + big, (hb.d1 + lb.d1) + big);
         if (n_hi > 0)
-          store4<OUT32>(p.out, out_lo + Geom::kHiOffset / 2, ha.d2 + la.d2, ha.d3 + la.d3,
-                        hb.d2 + lb.d2, hb.d3 + lb.d3);
+          store4<OUT32>(p.out, out_lo + Geom::kHiOffset / 2, (ha.d2 + la.d2) + big, (ha.d3 + la.d3) + big,
+                        (hb.d2 + lb.d2) + big, (hb.d3 + lb.d3) + big);
       } else {
-        store_masked<OUT32>(p.out, out_lo, n_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
-                            hb.d1 + lb.d1);
-        store_masked<OUT32>(p.out, out_lo + Geom::kHiOffset / 2, n_hi, ha.d2 + la.d2,
-                            ha.d3 + la.d3, hb.d2 + lb.d2, hb.d3 + lb.d3);
+        store_masked<OUT32>(p.out, out_lo, n_lo, (ha.d0 + la.d0) + big, (ha.d1 + la.d1) + big, (hb.d0 + lb.d0) + big,
+                            (hb.d1 + lb.d1) + big);
+        store_masked<OUT32>(p.out, out_lo + Geom::kHiOffset / 2, n_hi, (ha.d2 + la.d2) + big,
+                            (ha.d3 + la.d3) + big, (hb.d2 + lb.d2) + big, (hb.d3 + lb.d3) + big);
       }
       carry += (double)step_h + (double)step_l;
     }

@@ -239,6 +239,10 @@ __device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const 
 // the running carry kept by fp32 adds instead of a dependent MMA: the totals of
 // this step come from MMAs with a zero accumulator, independent of every other
 // step, so consecutive steps overlap even with few warps per scheduler.
+// `big`: the part of the prefix before this slice that is too large to ride
+// through the accumulators without costing them their low bits (0 when there
+// is none); it is added once, last, so each output is rounded once at its own
+// magnitude.
 struct RowCarry {
   float h_lo, l_lo, h_hi, l_hi;  // (exact hi part, lo part) x (row g, row g+8)
 };
@@ -248,7 +252,7 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
                                                       const uint32_t (&al)[4],
                                                       const ScanOperands& ops, RowCarry& c,
                                                       void* out, unsigned long long elem_base,
-                                                      int valid_elems, int g, int t) {
+                                                      int valid_elems, int g, int t, float big) {
   using Geom = ScanGeom<SC>;
   const Acc zero{0.f, 0.f, 0.f, 0.f};
   const Acc c_h{c.h_lo, c.h_lo, c.h_hi, c.h_hi}, c_l{c.l_lo, c.l_lo, c.l_hi, c.l_hi};
@@ -265,11 +269,11 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
   }
   const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
   if (e_lo < valid_elems)
-    store4<OUT32, kStream>(out, elem_base + e_lo, ha.d0 + la.d0, ha.d1 + la.d1, hb.d0 + lb.d0,
-                  hb.d1 + lb.d1);
+    store4<OUT32, kStream>(out, elem_base + e_lo, (ha.d0 + la.d0) + big, (ha.d1 + la.d1) + big,
+                           (hb.d0 + lb.d0) + big, (hb.d1 + lb.d1) + big);
   if (e_hi < valid_elems)
-    store4<OUT32, kStream>(out, elem_base + e_hi, ha.d2 + la.d2, ha.d3 + la.d3, hb.d2 + lb.d2,
-                  hb.d3 + lb.d3);
+    store4<OUT32, kStream>(out, elem_base + e_hi, (ha.d2 + la.d2) + big, (ha.d3 + la.d3) + big,
+                           (hb.d2 + lb.d2) + big, (hb.d3 + lb.d3) + big);
 }
 
 // Segment classes as for the reduction: 4..11 = 2^class elements (inside one

@@ -447,12 +447,16 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     const SliceView v = slice_view(ring_b + b * kTileBytes, tile);
     double carry = tile_excl[q];
     for (int w = 0; w < cw; ++w) carry += (double)part[q][w].x + (double)part[q][w].y;
-    // Everything before this slice, as two floats that ride through the MMAs'
-    // accumulator operand with the row carries: xh a multiple of 2^-13 (what the
-    // hi parts are made of, so sums below 2^11 stay exact), xl the small rest.
+    // Everything before this slice, as two floats: xh a multiple of 2^-13 (what the
+    // hi parts are made of), xl the small rest.  While xh is below 2^10 it rides
+    // through the MMAs' accumulator operand with the row carries and every sum
+    // stays exact; a larger one would push the row sums out of the accumulator's
+    // 24 bits, so it is held back and added to each output last.
     const double carry_hi = rint(carry * 8192.0) * (1.0 / 8192.0);
     const float xh = (float)carry_hi;
     const float xl = (float)(carry - (double)xh);
+    const bool fold = fabsf(xh) < 1024.f;
+    const float xf = fold ? xh : 0.f, big = fold ? 0.f : xh;
     if (v.valid_bytes > 0) {
       if constexpr (!kSwz)
         if (v.valid_bytes < kSliceBytes) zero_slice_tail(v.slice, v.valid_bytes, lane);
@@ -472,7 +476,7 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
         float slice_h, slice_l;
         row_carries<16>(tot_h, tot_l, g, c.x, c.y, c.z, c.w, slice_h, slice_l);
       }
-      RowCarry rc{c.x + xh, c.y + xl, c.z + xh, c.w + xl};
+      RowCarry rc{c.x + xf, c.y + xl, c.z + xf, c.w + xl};
       const unsigned long long elem_base = v.slice_off / 2;
       const int valid_elems = v.valid_bytes / 2;
 #pragma unroll
@@ -480,7 +484,7 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
         uint32_t ah[4], al[4];
         load_split(addr, j, ah, al);
         scan_step_independent<SC, OUT32, TCU_LB_STREAM_STORES != 0>(j, ah, al, ops, rc, p.out, elem_base,
-                                                                    valid_elems, g, t);
+                                                                    valid_elems, g, t, big);
       }
     }
     __syncwarp();
