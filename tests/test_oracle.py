@@ -135,3 +135,25 @@ def test_cpu_baseline_within_tolerance():
     fs = np.empty(y.size, dtype=np.float32)
     lib.tcu_cpu_full_scan(y.ctypes.data, fs.ctypes.data, y.size, 3)
     assert oracle.np_check_f32(fs, oracle.np_segmented_scan(y, y.size))[0] == 0
+
+
+def test_bf16_side_of_the_oracle_agrees_with_torch_on_cpu():
+    """The bfloat16 conversions of the oracle against an independent implementation."""
+    import torch
+    rng = np.random.default_rng(5)
+    v = np.concatenate([rng.uniform(-1, 1, 4096), rng.uniform(-1e-6, 1e-6, 512), [0.0, 1.0, -1.0, 0.001,
+                        1.0 + 2.0 ** -8, 1.0 + 3 * 2.0 ** -9]]).astype(np.float32)  # incl. rounding ties
+    mine = oracle.f32_to_bf16_bits(v)
+    theirs = torch.from_numpy(v).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(mine, theirs)
+    back = torch.from_numpy(mine.view(np.int16)).view(torch.bfloat16).double().numpy()
+    assert np.array_equal(oracle._as_f64(mine, "bf16"), back)
+    x = oracle.np_fill_f16(1 << 12, 9, 0, "uniform_pm1", fmt="bf16")
+    t = torch.from_numpy(x.view(np.int16)).view(torch.bfloat16).double()
+    assert np.array_equal(oracle.np_segmented_reduce(x, 64, fmt="bf16"), t.view(-1, 64).sum(1).numpy())
+    assert np.allclose(oracle.np_segmented_scan(x, 256, fmt="bf16"),
+                       torch.cumsum(t.view(-1, 256), 1).reshape(-1).numpy(), rtol=0, atol=1e-12)
+    # a correctly rounded bfloat16 is zero representable values away from itself, its neighbour one
+    ref = oracle._as_f64(x, "bf16")
+    assert oracle.np_check_f16(x, ref, 0, fmt="bf16") == (0, 0)
+    assert oracle.np_check_f16(x + np.uint16(1), ref, 0, fmt="bf16")[1] == 1
