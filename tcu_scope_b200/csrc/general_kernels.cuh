@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_reduce_general_kernel(con
   pdl_prologue();
   const int lane = threadIdx.x & 31;
   const unsigned long long warps = (unsigned long long)gridDim.x * (kGeneralThreads / 32);
-  const unsigned long long first = (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
+  const unsigned long long first =
+      (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
   const unsigned long long vecs  = (seg_elems + 7) / 8;  // groups of 8 elements per segment
   const Acc zero{0.f, 0.f, 0.f, 0.f};
   constexpr int kFlushEvery = 64;  // 64 steps x 16 elements per row: sums below 2^11 stay exact
@@ -119,7 +120,8 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
   static_assert(Geom::kLinear, "the general scan relies on the linear 16-element rows");
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const unsigned long long warps = (unsigned long long)gridDim.x * (kGeneralThreads / 32);
-  const unsigned long long first = (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
+  const unsigned long long first =
+      (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
   const unsigned long long num_segments = p.num_elems / seg_elems;
   const ScanOperands ops = make_scan_operands(lane, p.exclusive != 0);
   const Acc zero{0.f, 0.f, 0.f, 0.f};
@@ -165,17 +167,17 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
       const Acc la = mma16816(al[0], al[1], al[2], al[3], ops.ua0, ops.ua1, c_l);
       const Acc lb = mma16816(al[0], al[1], al[2], al[3], ops.ub0, ops.ub1, c_l);
       const unsigned long long out_lo = seg_base + e0 + off_lo / 2;
+      const unsigned long long out_hi = out_lo + Geom::kHiOffset / 2;
+      const float r0 = (ha.d0 + la.d0) + big, r1 = (ha.d1 + la.d1) + big;  // row g, 4 outputs
+      const float r2 = (hb.d0 + lb.d0) + big, r3 = (hb.d1 + lb.d1) + big;
+      const float q0 = (ha.d2 + la.d2) + big, q1 = (ha.d3 + la.d3) + big;  // row g + 8
+      const float q2 = (hb.d2 + lb.d2) + big, q3 = (hb.d3 + lb.d3) + big;
       if constexpr (kVec) {
-        if (n_lo > 0)
-          store4<OUT32>(p.out, out_lo, (ha.d0 + la.d0) + big, (ha.d1 + la.d1) + big, (hb.d0 + lb.d0) + big, (hb.d1 + lb.d1) + big);
-        if (n_hi > 0)
-          store4<OUT32>(p.out, out_lo + Geom::kHiOffset / 2, (ha.d2 + la.d2) + big, (ha.d3 + la.d3) + big,
-                        (hb.d2 + lb.d2) + big, (hb.d3 + lb.d3) + big);
+        if (n_lo > 0) store4<OUT32>(p.out, out_lo, r0, r1, r2, r3);
+        if (n_hi > 0) store4<OUT32>(p.out, out_hi, q0, q1, q2, q3);
       } else {
-        store_masked<OUT32>(p.out, out_lo, n_lo, (ha.d0 + la.d0) + big, (ha.d1 + la.d1) + big, (hb.d0 + lb.d0) + big,
-                            (hb.d1 + lb.d1) + big);
-        store_masked<OUT32>(p.out, out_lo + Geom::kHiOffset / 2, n_hi, (ha.d2 + la.d2) + big,
-                            (ha.d3 + la.d3) + big, (hb.d2 + lb.d2) + big, (hb.d3 + lb.d3) + big);
+        store_masked<OUT32>(p.out, out_lo, n_lo, r0, r1, r2, r3);
+        store_masked<OUT32>(p.out, out_hi, n_hi, q0, q1, q2, q3);
       }
       carry += (double)step_h + (double)step_l;
     }

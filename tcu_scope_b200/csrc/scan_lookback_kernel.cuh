@@ -80,7 +80,6 @@ constexpr uint32_t kNoEnd = 0xffffffffu;
 // [8] in-block walk ns [9] block walk ns [10] in-block empty polls [11] block empty polls
 // [12] ns from the tile's ticket to the start of its look-back
 __device__ unsigned long long g_lb_stats[16];
-__device__ unsigned long long g_lb_polls_scratch;
 __device__ __forceinline__ unsigned long long gtime() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -116,7 +116,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   for (int idx = threadIdx.x; idx < kUmmaN * kSwizzleRowElems; idx += kUmmaThreads) {
     const int n = idx / kSwizzleRowElems, k = idx % kSwizzleRowElems;
     const bool one = n < kSegsPerRow && (k >> LOG2S) == n;
-    *reinterpret_cast<uint16_t*>(bmat + swizzle128(n * 128 + k * 2)) = one ? static_cast<uint16_t>(kOne16) : uint16_t(0);
+    *reinterpret_cast<uint16_t*>(bmat + swizzle128(n * 128 + k * 2)) =
+        one ? static_cast<uint16_t>(kOne16) : uint16_t(0);
   }
   // make the generic-proxy writes of B visible to the tensor core's async reads
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
