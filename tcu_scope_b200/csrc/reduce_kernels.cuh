@@ -231,19 +231,7 @@ template <int SC, bool kTensor = true>
 __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReduceParams p) {
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kStages];
-#ifndef TCU_REDUCE_LAST_ARRIVER
-#define TCU_REDUCE_LAST_ARRIVER 0
-#endif
-  // Classes 12..14: a segment spans 2/4/8 slices of a tile.  The warps do not
-  // meet at a barrier: each leaves its slice total in a slot and counts itself
-  // in; whichever warp of the segment arrives last adds the totals up (in slice
-  // order, so the result does not depend on who that was).  A warp is never
-  // more than kStages tiles ahead of the slowest one -- a stage is refilled only
-  // after all eight released it -- so 2 * kStages slots cannot collide.
-  constexpr bool kLastArriver = SC >= 12 && SC <= 14 && TCU_REDUCE_LAST_ARRIVER != 0;
-  constexpr int kPartSlots    = kLastArriver ? 2 * kStages : 2;
-  __shared__ float2 part[kPartSlots][kConsumerWarps];  // slice totals of the tiles in flight
-  __shared__ unsigned int part_count[kPartSlots][4];   // warps of a segment that have arrived
+  __shared__ float2 part[2][kConsumerWarps];  // slice totals of the tile in flight
   __shared__ double warp_sum[2][kConsumerWarps];  // long class: per-warp running sums of a segment
   __shared__ int s_is_last;
 
@@ -260,7 +248,6 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
     }
     mbar_fence_init();
   }
-  if (threadIdx.x < kPartSlots * 4) (&part_count[0][0])[threadIdx.x] = 0u;
   __syncthreads();
   pdl_prologue();  // nothing above touched global memory
 
@@ -382,39 +369,17 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
         run_val += (double)tot.x + (double)tot.y;
       } else if constexpr (SC >= 12) {
         // combine the slice totals of this tile across warps
-        constexpr int kWarpsPerSeg = SC == 12 ? 2 : (SC == 13 ? 4 : 8);
-        if constexpr (kLastArriver) {
-          const uint32_t slot = i % kPartSlots;
-          const int grp = warp / kWarpsPerSeg;
-          unsigned int arrived = 0;
-          if (lane == 0) {
-            part[slot][warp] = tot;
-            __threadfence_block();
-            arrived = atomicAdd(&part_count[slot][grp], 1u);
-          }
-          arrived = __shfl_sync(0xffffffffu, arrived, 0);
-          if (arrived == kWarpsPerSeg - 1) {  // every slice of the segment is in
-            __threadfence_block();
-            if (lane == 0) part_count[slot][grp] = 0u;  // next use is at least kStages tiles away
-            const float2 pr = part[slot][grp * kWarpsPerSeg + (lane & (kWarpsPerSeg - 1))];
-            double v = (double)pr.x + (double)pr.y;
+        if (lane == 0) part[i & 1][warp] = tot;
+        consumer_sync();
+        if (warp == 0) {
+          const float2 pr = part[i & 1][lane & 7];
+          double v = (double)pr.x + (double)pr.y;
+          constexpr int kWarpsPerSeg = SC == 12 ? 2 : (SC == 13 ? 4 : 8);
 #pragma unroll
-            for (int m = 1; m < kWarpsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-            const unsigned long long seg = tile * (8 / kWarpsPerSeg) + grp;
-            if (lane == 0 && seg < p.num_segments && !dead) store_seg(p.out, out_f32, seg, (float)v);
-          }
-        } else {
-          if (lane == 0) part[i & 1][warp] = tot;
-          consumer_sync();
-          if (warp == 0) {
-            const float2 pr = part[i & 1][lane & 7];
-            double v = (double)pr.x + (double)pr.y;
-#pragma unroll
-            for (int m = 1; m < kWarpsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-            const unsigned long long seg = tile * (8 / kWarpsPerSeg) + lane / kWarpsPerSeg;
-            if (lane < 8 && (lane % kWarpsPerSeg) == 0 && seg < p.num_segments && !dead)
-              store_seg(p.out, out_f32, seg, (float)v);
-          }
+          for (int m = 1; m < kWarpsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+          const unsigned long long seg = tile * (8 / kWarpsPerSeg) + lane / kWarpsPerSeg;
+          if (lane < 8 && (lane % kWarpsPerSeg) == 0 && seg < p.num_segments && !dead)
+            store_seg(p.out, out_f32, seg, (float)v);
         }
       }
     }
