@@ -421,7 +421,7 @@ int main(int argc, char** argv) {
     else if (flag_value(argv[i], "--fill", &v)) o.const_fill = v == "const";
     else if (flag_value(argv[i], "--validate", &v)) o.validate = v != "false";
     else if (flag_value(argv[i], "--cold_cache", &v)) o.cold_cache = v != "false" && v != "0";
-    else if (flag_value(argv[i], "--algo", &v)) o.algo = v == "shuffle" ? TCU_ALGO_SHUFFLE : TCU_ALGO_MMA;
+    else if (flag_value(argv[i], "--algo", &v)) o.algo = v == "shuffle" ? TCU_ALGO_SHUFFLE : v == "tcgen05" ? TCU_ALGO_TCGEN05 : TCU_ALGO_MMA;
     else if (flag_value(argv[i], "--out_type", &v)) o.out_type = v == "f32" ? TCU_OUT_F32 : TCU_OUT_F16;
     else if (flag_value(argv[i], "--min_log2", &v)) o.min_log2 = std::atoi(v.c_str());
     else if (flag_value(argv[i], "--max_log2", &v)) o.max_log2 = std::atoi(v.c_str());
@@ -430,7 +430,7 @@ int main(int argc, char** argv) {
                   "[--benchmark_out=FILE] [--benchmark_min_time=S]\n"
                   "                 [--cuda_device_id=N] [--seed=N] [--fill=uniform|const] [--validate] "
                   "[--cold_cache=0|1]\n"
-                  "                 [--algo=mma|shuffle] [--out_type=f16|f32] [--min_log2=N] [--max_log2=N]\n");
+                  "                 [--algo=mma|shuffle|tcgen05] [--out_type=f16|f32] [--min_log2=N] [--max_log2=N]\n");
       return std::strcmp(argv[i], "-h") == 0 || std::strcmp(argv[i], "--help") == 0 ? 0 : 1;
     }
   }
