@@ -467,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
 #ifndef TCU_SCAN_S16_F16_UNSPLIT
 #define TCU_SCAN_S16_F16_UNSPLIT 0
 #endif
-      if constexpr (SC == 4 && !OUT32 && TCU_SCAN_S16_F16_UNSPLIT != 0) {
+      if constexpr (SC == 4 && (!OUT32 || TCU_SCAN_S16_F16_UNSPLIT == 2) && TCU_SCAN_S16_F16_UNSPLIT != 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const uint8_t* src = addr.lo(j);
