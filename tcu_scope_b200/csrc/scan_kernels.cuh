@@ -235,25 +235,6 @@ __device__ __forceinline__ void scan_step(int j, const uint32_t (&ah)[4], const 
                   hb.d3 + lb.d3);
 }
 
-// 16-element segments, fp16 outputs: one step without the hi/lo split.  A sum
-// of at most 16 halves of magnitude <= 1 is a sum of multiples of 2^-24 below
-// 16, which the tensor core's fp32 accumulation delivers rounded once; the
-// fp16 rounding of the output is 2^13 times coarser.  Half the MMAs and none of
-// the split arithmetic of scan_step.
-template <bool OUT32>
-__device__ __forceinline__ void scan_step_s16_unsplit(int j, const uint2 lo, const uint2 hi,
-                                                      const ScanOperands& ops, void* out,
-                                                      unsigned long long elem_base,
-                                                      int valid_elems, int g, int t) {
-  using Geom = ScanGeom<4>;
-  const Acc zero{0.f, 0.f, 0.f, 0.f};
-  const Acc a = mma16816(lo.x, hi.x, lo.y, hi.y, ops.ua0, ops.ua1, zero);
-  const Acc b = mma16816(lo.x, hi.x, lo.y, hi.y, ops.ub0, ops.ub1, zero);
-  const int e_lo = Geom::lo(g, t, j) / 2, e_hi = e_lo + Geom::kHiOffset / 2;
-  if (e_lo < valid_elems) store4<OUT32>(out, elem_base + e_lo, a.d0, a.d1, b.d0, b.d1);
-  if (e_hi < valid_elems) store4<OUT32>(out, elem_base + e_hi, a.d2, a.d3, b.d2, b.d3);
-}
-
 // Variant of scan_step for rows that are chained over all eight steps, with
 // the running carry kept by fp32 adds instead of a dependent MMA: the totals of
 // this step come from MMAs with a zero accumulator, independent of every other
@@ -464,17 +445,6 @@ __global__ void __launch_bounds__(kThreads, scan_ctas_per_sm(SC)) seg_scan_kerne
     if (active) {
       const unsigned long long elem_base = slice_off / 2;
       const int valid_elems = valid_bytes / 2;
-#ifndef TCU_SCAN_S16_F16_UNSPLIT
-#define TCU_SCAN_S16_F16_UNSPLIT 0
-#endif
-      if constexpr (SC == 4 && (!OUT32 || TCU_SCAN_S16_F16_UNSPLIT == 2) && TCU_SCAN_S16_F16_UNSPLIT != 0) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint8_t* src = addr.lo(j);
-          scan_step_s16_unsplit<OUT32>(j, lds64(src), lds64(src + Geom::kHiOffset), ops, p.out,
-                                       elem_base, valid_elems, g, t);
-        }
-      } else
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if constexpr (!kScanCache) load_split(addr, j, ah[0], al[0]);  // second read
