@@ -33,7 +33,7 @@ LOG2_ELEMS = 28
 SWEEP = [16, 32, 64, 256, 1024, 16384]
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 # dram__bytes_read.sum + dram__bytes_write.sum of one seg_reduce_kernel<4> launch: captured by
-# ncu at 2^27 elements (268.461 MB read + 25.693 MB written, profiles/seg_reduce_kernel_sweep_2p27.md)
+# ncu at 2^27 elements (268.461 MB read + 25.693 MB written; the capture is summarised under profiles/)
 # and doubled for the 2^28-element launch of this benchmark (traffic grows with the element count).
 NCU_TRAFFIC_BYTES_S16 = 2 * (268_460_800 + 25_693_440)
 
