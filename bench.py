@@ -45,7 +45,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--algo", default="auto", choices=["auto", "mma", "shuffle", "tcgen05"],
-                    help="tcgen05 only exists for segment sizes 16/32/64: use it with --profile reduce")
+                    help="tcgen05 only exists for segment sizes up to 2048: use it with --profile reduce")
     ap.add_argument("--log2-elems", type=int, default=LOG2_ELEMS,
                     help="elements per GPU (default 28, the reference sweep's size)")
     ap.add_argument("--profile", default=None, choices=["reduce", "scan", "full"],
@@ -55,7 +55,7 @@ def parse_args():
                     help="skip the other configurations, the e2e leg and the CPU baseline")
     args = ap.parse_args()
     if args.algo == "tcgen05" and args.profile != "reduce":
-        ap.error("--algo tcgen05 covers segment sizes 16/32/64 only: use it with --profile reduce "
+        ap.error("--algo tcgen05 covers segment sizes up to 2048 only: use it with --profile reduce "
                  "(the timed sweep reports it under ablation_tensor_core_vs_shuffle)")
     return args
 
@@ -442,7 +442,7 @@ def cub_leg(torch, tcu, args):
 def ablation_leg(torch, tcu, args):
     """In-run ablation: the same TMA pipeline with CUDA-core adds and warp shuffles in place of
     the tensor-core contraction (TCU_ALGO_SHUFFLE), on the sweep and on the segmented scans, and
-    the tcgen05 / tensor-memory form of the 16/32/64-element reductions (TCU_ALGO_TCGEN05)."""
+    the tcgen05 / tensor-memory form of the reductions up to 2048 elements (TCU_ALGO_TCGEN05)."""
     n = 1 << min(args.log2_elems, 28)
     xs = [tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024 + i, 0) for i in range(2)]
     k = [0]
@@ -472,7 +472,7 @@ def ablation_leg(torch, tcu, args):
             del o
         out["scan"][algo] = sc
     red = {}
-    for s in (16, 32, 64):
+    for s in [v for v in SWEEP if v <= 2048]:
         o = torch.empty(n // s, dtype=torch.float32, device="cuda")
 
         def call():
@@ -483,7 +483,8 @@ def ablation_leg(torch, tcu, args):
     out["reduce"]["tcgen05"] = red
     out["note"] = ("direct launches, CUDA events around 10 back-to-back calls; the shuffle variant "
                    "does not split inputs into exact parts (plain fp32 rounding); tcgen05 = "
-                   "tcgen05.mma with the accumulator in tensor memory, segment sizes 16/32/64 only")
+                   "tcgen05.mma with the accumulator in tensor memory, segment sizes up to 2048 (plain fp32 "
+                   "accumulation, no exact parts)")
     return out
 
 
@@ -531,7 +532,7 @@ def profile_pass(torch, tcu, args, n, json_fd):
     """One launch of each kernel of a family, for a profiler to capture."""
     x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 2024, 0)
     if args.profile == "reduce":
-        for s in (SWEEP if args.algo != "tcgen05" else (16, 32, 64)):
+        for s in (SWEEP if args.algo != "tcgen05" else [v for v in SWEEP if v <= 2048]):
             tcu.segmented_reduce(x, s, algo=args.algo)
     elif args.profile == "scan":
         for s, dt in [(16, torch.float16), (256, torch.float16), (4096, torch.float32)]:

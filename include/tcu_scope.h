@@ -44,7 +44,8 @@ typedef enum {
   TCU_ALGO_MMA     = 1, /* TMA ring + mma.sync m16n8k16 against ones / triangular ones  */
   TCU_ALGO_SHUFFLE = 2, /* same pipeline, CUDA-core adds + warp shuffles: the ablation  */
   TCU_ALGO_TCGEN05 = 3  /* tcgen05.mma, accumulators in tensor memory: segmented
-                           reduction of 16/32/64-element segments, num_elements % 64 == 0 */
+                           reduction of 16 ... 2048-element segments (powers of two),
+                           num_elements % 64 == 0; plain fp32 accumulation */
 } tcu_algo;
 
 typedef enum { TCU_OUT_F16 = 0, TCU_OUT_F32 = 1 } tcu_out_type;

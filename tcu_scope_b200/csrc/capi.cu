@@ -267,8 +267,8 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   if (sc == kClassGeneral && algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA) return TCU_ERR_UNSUPPORTED;
   size_t n = 0;
   if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
-  // the tcgen05 variant covers 16/32/64-element segments of arrays it can view as 64-wide rows
-  if (algo == TCU_ALGO_TCGEN05 && (sc < 4 || sc > 6 || n % kSwizzleRowElems != 0))
+  // the tcgen05 variant covers 16 ... 2048-element segments of arrays it can view as 64-wide rows
+  if (algo == TCU_ALGO_TCGEN05 && (sc < 4 || sc > 11 || n % kSwizzleRowElems != 0))
     return TCU_ERR_UNSUPPORTED;
   if (n == 0) return TCU_OK;
   // short classes store vectors of outputs, the long and the general class single values
@@ -303,9 +303,12 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
     if (!make_input_tensor_map(&map, d_in, n, kUmmaRows)) return TCU_ERR_CUDA;
     const size_t utiles = (n + kUmmaTileElems - 1) / kUmmaTileElems;
     const int ugrid     = utiles < size_t(sms) ? int(utiles) : sms;
-    e = sc == 4   ? launch_tcgen05_reduce<4>(p, map, ugrid, st)
-        : sc == 5 ? launch_tcgen05_reduce<5>(p, map, ugrid, st)
-                  : launch_tcgen05_reduce<6>(p, map, ugrid, st);
+    switch (sc) {
+#define X(C) case C: e = launch_tcgen05_reduce<C>(p, map, ugrid, st); break;
+      X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11)
+#undef X
+      default: return TCU_ERR_UNSUPPORTED;
+    }
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   if (sc == kClassLong) {

@@ -1,10 +1,12 @@
-// Segmented reduction of short segments (16, 32, 64 elements) on the
+// Segmented reduction of segments of 16 ... 2048 elements on the
 // fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor
 // memory.  Same contraction as reduce_kernels.cuh -- rows of the input times a
 // constant 0/1 matrix -- but issued the Blackwell way: one thread launches
 // M=128 x N=16 x K=16 MMAs that read both operands straight from shared memory
 // (no register fragments), four MMAs cover a 128 x 64 tile (16 KiB), and four
-// epilogue warps read the sums back with tcgen05.ld, one output row per thread.
+// epilogue warps read the sums back with tcgen05.ld, one output row per thread
+// (segments of 128 elements and more are 2 ... 32 rows: the epilogue adds the
+// row sums of neighbouring lanes with shuffles).
 //
 //   A (128 x 64 halves, K-major): tile rows = 64 consecutive input halves,
 //       loaded by a swizzled tensor-map TMA copy (SWIZZLE_128B).
@@ -85,8 +87,10 @@ __device__ __forceinline__ void tcgen05_fence_after_sync() {
 template <int LOG2S>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
     tcgen05_reduce_kernel(const ReduceParams p, const __grid_constant__ CUtensorMap tmap) {
-  static_assert(LOG2S >= 4 && LOG2S <= 6, "16, 32 or 64 elements per segment");
-  constexpr int kSegsPerRow = kSwizzleRowElems >> LOG2S;  // 4, 2, 1 sums per 64-element row
+  static_assert(LOG2S >= 4 && LOG2S <= 11, "16 ... 2048 elements per segment");
+  // 4, 2 or 1 sums per 64-element row; from 128 elements on a segment is 2 ... 32 whole rows
+  constexpr int kSegsPerRow = LOG2S <= 6 ? (kSwizzleRowElems >> LOG2S) : 1;
+  constexpr int kRowsPerSeg = LOG2S <= 6 ? 1 : (1 << (LOG2S - 6));
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kUmmaStages + 2 * kUmmaAccStages];
   __shared__ uint32_t s_tmem_base;
@@ -184,6 +188,17 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * a);  // values are in registers now
       const unsigned long long row = tile * kUmmaRows + quarter * 32 + lane;
+      if constexpr (kRowsPerSeg > 1) {
+        // a segment is kRowsPerSeg consecutive rows = consecutive lanes of this warp: add the row
+        // sums up in double (rows past the end of the array are zeros and join harmlessly)
+        double v = static_cast<double>(__uint_as_float(r0));
+#pragma unroll
+        for (int m = 1; m < kRowsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+        const unsigned long long seg = row / kRowsPerSeg;
+        if ((lane & (kRowsPerSeg - 1)) == 0 && seg < p.num_segments)
+          store_seg(p.out, out_f32, seg, static_cast<float>(v));
+        continue;
+      }
       const unsigned long long seg = row * kSegsPerRow;
       if (seg < p.num_segments) {  // rows past the end of the array hold zeros: not stored
         const float v0 = __uint_as_float(r0), v1 = __uint_as_float(r1);

@@ -1,4 +1,4 @@
-"""The tcgen05 / tensor-memory variant of the short-segment reduction (TCU_ALGO_TCGEN05)
+"""The tcgen05 / tensor-memory variant of the segmented reduction (TCU_ALGO_TCGEN05, segments of 16 ... 2048)
 against the oracle and against the mma.sync path."""
 import numpy as np
 import pytest
@@ -13,12 +13,13 @@ def bits(t):
     return t.cpu().view(torch.int16).numpy().view(np.uint16)
 
 
-@pytest.mark.parametrize("s", [16, 32, 64])
+@pytest.mark.parametrize("s", [16, 32, 64, 128, 256, 512, 1024, 2048])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
 def test_tcgen05_reduce_matches_oracle(s, out_dtype):
     import tcu_scope_b200 as tcu
     # one row, a partial tile, whole tiles, many tiles per SM (ring and accumulators wrap)
     for n in (64, 64 * 37, 8192, 8192 * 5 + 64 * 3, 1 << 20, (1 << 25) + 64 * 11):
+        n = max(s, n // s * s)  # whole segments (and still whole 64-element rows)
         x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 70 + s, 0)
         buf = torch.full((n // s + 128,), -777.0, dtype=out_dtype, device="cuda")
         out = buf[64:64 + n // s]
@@ -40,7 +41,7 @@ def test_tcgen05_rejects_what_it_does_not_cover():
     import tcu_scope_b200 as tcu
     x = tcu.fill(torch.empty(4096, dtype=torch.float16, device="cuda"), 1, 0)
     with pytest.raises(tcu.TcuError) as e:
-        tcu.segmented_reduce(x, 256, algo="tcgen05")  # only 16/32/64-element segments
+        tcu.segmented_reduce(x, 4096, algo="tcgen05")  # only segments of 16 ... 2048 elements
     assert e.value.status == 2
     with pytest.raises(tcu.TcuError):
         tcu.segmented_reduce(x[:4096 - 16], 16, algo="tcgen05")  # element count not a multiple of 64
