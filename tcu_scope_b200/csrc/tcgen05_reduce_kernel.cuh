@@ -115,6 +115,21 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     }
     s_failed = 0u;
     mbar_fence_init();
+#ifndef TCU_UMMA_EARLY_LOADS
+#define TCU_UMMA_EARLY_LOADS 1
+#endif
+    if constexpr (TCU_UMMA_EARLY_LOADS != 0) {
+      // This thread is also the producer: it fills the ring right away, so the first tiles are
+      // in flight while the others build B and allocate tensor memory.
+      pdl_prologue();
+      const unsigned long long rows  = p.num_elems / kSwizzleRowElems;
+      const unsigned long long tiles = (rows + kUmmaRows - 1) / kUmmaRows;
+      unsigned long long tile = blockIdx.x;
+      for (int s = 0; s < kUmmaStages && tile < tiles; ++s, tile += gridDim.x) {
+        mbar_arrive_expect_tx(full0 + 8 * s, kUmmaTileBytes);
+        tma_load_2d(tiles_u32 + s * kUmmaTileBytes, &tmap, 0, (int)(tile * kUmmaRows), full0 + 8 * s);
+      }
+    }
   }
   // B operand, written through the same 128-byte swizzle the MMA expects.
   for (int idx = threadIdx.x; idx < kUmmaN * kSwizzleRowElems; idx += kUmmaThreads) {
@@ -142,8 +157,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t i = 0;
-      for (unsigned long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
+      // the first kUmmaStages tiles were requested before the CTA-wide set-up (see above)
+      uint32_t i = TCU_UMMA_EARLY_LOADS != 0 ? kUmmaStages : 0;
+      for (unsigned long long tile = blockIdx.x + (unsigned long long)i * gridDim.x; tile < num_tiles;
+           tile += gridDim.x, ++i) {
         const uint32_t s = i % kUmmaStages, ph = (i / kUmmaStages) & 1u;
         if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) { s_failed = 1u; break; }
         mbar_arrive_expect_tx(full0 + 8 * s, kUmmaTileBytes);  // rows past the end arrive as zeros
