@@ -7,7 +7,10 @@ fp32 per-segment sums at segment sizes 16, 32, 64, 256, 1024 and 16384 (six
 launches).  Segments are sharded over the GPUs with no communication (weak
 scaling: every GPU holds its own 2^28 elements).  Throughput is elements
 processed per second, the reference's counter
-(src/reduction/seg_wmma_16n.cu:75-81), in Gelem/s.
+(src/reduction/seg_wmma_16n.cu:75-81), in Gelem/s.  With more than one GPU the
+line also carries the strong-scaling form of every configuration (the fixed
+totals of the benchmark definition cut into one shard per GPU), each with its
+outputs checked against the fp64 oracle on every rank.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -32,11 +35,33 @@ sys.path.insert(0, ROOT)
 LOG2_ELEMS = 28
 SWEEP = [16, 32, 64, 256, 1024, 16384]
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
-# dram__bytes_read.sum + dram__bytes_write.sum of one seg_reduce_kernel<4> launch: captured by
-# ncu at 2^27 elements (268.461 MB read + 25.693 MB written; the capture is summarised under profiles/)
-# and doubled for the 2^28-element launch of this benchmark (traffic grows with the element count).
-NCU_TRAFFIC_BYTES_S16 = 2 * (268_460_800 + 25_693_440)
+NOMINAL_HBM_GBS = 8000.0   # the HBM figure the benchmark definition quotes its target against
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "seg_reduce_kernel_S16_traffic.json")
+KERNEL_SOURCES = ["tcu_scope_b200/csrc/common.cuh", "tcu_scope_b200/csrc/reduce_kernels.cuh"]
 
+
+def kernel_source_hash():
+    import hashlib
+    h = hashlib.sha256()
+    for rel in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, rel), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic(n_elems: int):
+    """DRAM bytes of one seg_reduce_kernel<4> launch over n_elems elements, scaled from the ncu
+    capture recorded next to its summary (traffic grows with the element count; the full-size
+    launch is too large to capture).  None, with the reason, when the record is missing or was
+    taken from other kernel sources than the ones this run was built from."""
+    try:
+        rec = json.load(open(TRAFFIC_FILE))
+    except Exception:
+        return None, "no capture recorded"
+    if rec.get("kernel_source_sha16") != kernel_source_hash():
+        return None, "capture predates the current kernel sources"
+    per_elem = (rec["dram_bytes_read"] + rec["dram_bytes_write"]) / float(1 << rec["log2_elems"])
+    return int(per_elem * n_elems), f"ncu capture at 2^{rec['log2_elems']} elements, scaled"
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -156,7 +181,7 @@ def run_reference_arm(args, rank: int, json_fd: int):
     import numpy as np
     import oracle
     lib = oracle.c_lib()
-    log2_sample = min(args.log2_elems, 26)
+    log2_sample = args.log2_elems  # the same 2^28 elements per size as the GPU arm
     n = 1 << log2_sample
     x = oracle.c_fill_f16(n, 2024, 0, "uniform_pm1")
     outs = {s: np.empty(n // s, dtype=np.float32) for s in SWEEP}
@@ -179,7 +204,9 @@ def run_reference_arm(args, rank: int, json_fd: int):
         "unit": "Gelem/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, 1),
+        "config": dict(workload_config(args, 1), sharding="one host, all cores, whole segments per thread",
+                       l2="host memory", timing="wall clock around the K steps",
+                       algo="plain C loops (oracle/tcu_oracle.c), fp32 accumulate"),
         "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0,
@@ -246,8 +273,49 @@ def time_graph(torch, fn, launches_per_graph: int, replays: int):
     return statistics.mean(out), min(out)
 
 
-def extras(torch, tcu, dist, args, rank, world, peak_gbs):
-    """The other configurations of the benchmark definition, a few repetitions each."""
+def time_rotating(torch, launch, nbuf: int, replays: int):
+    """launch(i) queues one kernel on buffer set i; one CUDA graph holds 12 launches or more,
+    cycling over the buffer sets (so consecutive launches never touch the same data and nbuf
+    sets exceed twice the L2; the cost of starting a graph is spread over a dozen kernels),
+    replayed `replays` times between two events.  Returns ms per launch (mean of 2 batches, best)."""
+    per_graph = -(-12 // nbuf) * nbuf
+    for i in range(nbuf):
+        launch(i)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for i in range(per_graph):
+                launch(i % nbuf)
+    torch.cuda.current_stream().wait_stream(side)
+    g.replay()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(2):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) / (replays * per_graph))
+    return statistics.mean(out), min(out)
+
+
+def max_over_ranks(torch, dist, world, *vals):
+    if world == 1:
+        return vals
+    t = torch.tensor(list(vals), dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return tuple(t.tolist())
+
+
+def extras(torch, tcu, dist, args, rank, world, peak_gbs, sweep_gelem_per_gpu):
+    """The other configurations of the benchmark definition, a few repetitions each.  With one
+    GPU: every configuration at its stated size.  With several: the same per-GPU sizes (weak
+    scaling) here, the stated totals cut into shards (strong scaling) in strong_scaling()."""
     out = {}
     dev = torch.device("cuda")
     n28 = 1 << min(args.log2_elems, 28)
@@ -259,7 +327,9 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
         g = gelem(n, ms_med)  # n = elements over all `gpus` GPUs; hbm_frac is per GPU
         return {"gelem_per_s": round(g, 1), "gelem_per_s_best": round(gelem(n, ms_min), 1),
                 "gbytes_per_s": round(g * bytes_per_elem, 1),
-                "hbm_frac": round(g * bytes_per_elem / peak_gbs / gpus, 4), "ms": round(ms_med, 4)}
+                "hbm_frac": round(g * bytes_per_elem / peak_gbs / gpus, 4),
+                "hbm_frac_of_nominal_8tbs": round(g * bytes_per_elem / NOMINAL_HBM_GBS / gpus, 4),
+                "ms": round(ms_med, 4)}
 
     # C1: 2^24 elements, S=16, cold cache: rotate over 8 buffer sets (256 MiB of input > 2x L2)
     n24 = 1 << 24
@@ -272,25 +342,22 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
         k[0] += 1
         tcu.segmented_reduce(xs[i], 16, out=os_[i], algo=args.algo)
     out["C1_seg_reduce_2^24_S16_cold"] = entry(n24, 2.25, *time_graph(torch, c1, 16, 10))
-    out["C1_seg_reduce_2^24_S16_cold"]["timing"] = "16 launches per CUDA graph, 8 rotating buffer sets"
-    # context for a launch this short: a plain device-to-device copy moving the same 37.7 MB
-    # (half read, half written), timed the same way -- what the box gives ANY kernel of this size
-    half = n24 * 9 // 16  # halves: 2 B read + 2 B written each = 2.25 B x 2^24
-    dsts = [torch.empty(half, dtype=torch.float16, device=dev) for _ in range(8)]
-
-    def copy_same_bytes():
-        i = k[0] % 8
-        k[0] += 1
-        dsts[i].copy_(xs[(i + 3) % 8][:half])
     c1_entry = out["C1_seg_reduce_2^24_S16_cold"]
-    try:
-        ms_copy, _ = time_graph(torch, copy_same_bytes, 16, 10)
-        c1_entry["copy_of_same_bytes_ms"] = round(ms_copy, 4)
-        c1_entry["frac_of_copy_at_this_size"] = round(ms_copy / c1_entry["ms"], 3)
-    except RuntimeError as e:  # context only: never fail the run for it
-        c1_entry["copy_of_same_bytes_ms"] = None
-        print(f"copy context skipped: {e}", file=sys.stderr)
-    del xs, os_, dsts
+    c1_entry["timing"] = "16 launches per CUDA graph, 8 rotating buffer sets"
+    # What bounds a launch this short: its HBM time plus the fixed cost of ANY launch of this
+    # shape in this graph, measured with the same kernel on an input of one tile per CTA
+    # (every CTA starts, loads once and leaves: launch, ramp and drain, next to no data).
+    tiny_n = tcu.num_sms() * 16384
+    tiny_x = tcu.fill(torch.empty(tiny_n, dtype=torch.float16, device=dev), 1, 0)
+    tiny_o = torch.empty(tiny_n // 16, dtype=torch.float32, device=dev)
+    ms_fixed, _ = time_graph(torch, lambda: tcu.segmented_reduce(tiny_x, 16, out=tiny_o, algo=args.algo), 16, 10)
+    hbm_ms = n24 * 2.25 / (peak_gbs * 1e9) * 1e3
+    c1_entry["fixed_cost_ms"] = round(ms_fixed, 4)
+    c1_entry["hbm_time_ms"] = round(hbm_ms, 4)
+    c1_entry["bound_ms"] = round(ms_fixed + hbm_ms, 4)
+    c1_entry["note"] = ("fixed_cost_ms = the same kernel on one tile per CTA in the same kind of graph; "
+                        "bound_ms = fixed cost + bytes / measured HBM peak")
+    del xs, os_, tiny_x, tiny_o
 
     x = [tcu.fill(torch.empty(n28, dtype=torch.float16, device=dev), 2, rank * n28 + i * (1 << 40))
          for i in range(2)]
@@ -307,46 +374,254 @@ def extras(torch, tcu, dist, args, rank, world, peak_gbs):
         del o
     del x
 
-    # C4 / C5: full reduce and full scan over 2^30 elements in total per GPU at N=1; with more
-    # GPUs each rank holds a contiguous 2^30-element shard and one all-gather of per-shard totals.
+    # C4 / C5: full reduce and full scan over 2^30 elements per GPU.  One GPU: the single-pass
+    # kernels.  More GPUs (weak scaling): each rank holds a contiguous 2^30-element shard; the
+    # totals travel either inside the kernels (PeerGroup) or through one all-gather per call.
     n30 = 1 << min(args.log2_elems + 2, 30)
     x = tcu.fill(torch.empty(n30, dtype=torch.float16, device=dev), 3, rank * n30, "uniform_01")
     ws = torch.empty(max(tcu.workspace_bytes(tcu.OP_FULL_SCAN, n30, n30),
                          tcu.workspace_bytes(tcu.OP_FULL_REDUCE, n30, n30)),
                      dtype=torch.uint8, device=dev)
     o32, o64 = torch.empty(1, dtype=torch.float32, device=dev), torch.empty(1, dtype=torch.float64, device=dev)
+    o = torch.empty(n30, dtype=torch.float32, device=dev)
 
     def local_total():
         tcu.full_reduce(x, workspace=ws, out=o32, out_f64=o64)
         return o64
 
-    def c4():
-        if world == 1:
-            local_total()  # one GPU: the kernel's own total is the result
-        else:
-            tcu.sharded_full_reduce(local_total)
-    ms_med, ms_min = time_op(torch, c4, 10)
-    if world > 1:
-        t = torch.tensor([ms_med, ms_min], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_med, ms_min = t.tolist()
-    out["C4_full_reduce_2^30_per_gpu"] = entry(n30 * world, 2, ms_med, ms_min, world)
+    ms = max_over_ranks(torch, dist, world, *time_op(torch, local_total, 10))
+    out["C4_full_reduce_2^30_one_gpu"] = entry(n30, 2, *ms)
+    ms = max_over_ranks(torch, dist, world, *time_op(
+        torch, lambda: tcu.full_scan(x, out=o, workspace=ws, algo=args.algo), 8))
+    out["C5_full_scan_2^30_one_gpu_f32"] = entry(n30, 6, *ms)
+    one_gpu = {"C2": round(sweep_gelem_per_gpu, 1),
+               "C4": out["C4_full_reduce_2^30_one_gpu"]["gelem_per_s"],
+               "C5": out["C5_full_scan_2^30_one_gpu_f32"]["gelem_per_s"]}
 
-    o = torch.empty(n30, dtype=torch.float32, device=dev)
-
-    def c5():
-        if world == 1:
-            tcu.full_scan(x, out=o, workspace=ws, algo=args.algo)
-        else:  # reduce pass -> all-gather of totals -> scan seeded with the earlier shards
-            tcu.sharded_full_scan(local_total, lambda totals, r: tcu.full_scan(
-                x, out=o, workspace=ws, shard_totals=totals, shard_index=r))
-    ms_med, ms_min = time_op(torch, c5, 8)
+    grp = tcu.PeerGroup()  # collective
+    # the two-pass scan of the multi-GPU path (reduce, then scan seeded by the earlier totals)
+    ms = max_over_ranks(torch, dist, world, *time_op(torch, lambda: grp.full_scan(x, out=o), 8))
+    key = "C5_full_scan_2^30_per_gpu_f32" if world > 1 else "C5_full_scan_2^30_two_pass_f32"
+    out[key] = entry(n30 * world, 6, *ms, world)
+    out[key]["exchange"] = "totals stored by the kernels into every rank's memory"
     if world > 1:
-        t = torch.tensor([ms_med, ms_min], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_med, ms_min = t.tolist()
-    out["C5_full_scan_2^30_per_gpu_f32"] = entry(n30 * world, 6, ms_med, ms_min, world)
+        ms = max_over_ranks(torch, dist, world, *time_op(torch, lambda: grp.full_reduce(x, out=o32, out_f64=o64), 10))
+        out["C4_full_reduce_2^30_per_gpu"] = entry(n30 * world, 2, *ms, world)
+        out["C4_full_reduce_2^30_per_gpu"]["exchange"] = "totals stored by the kernels into every rank's memory"
+        ms = max_over_ranks(torch, dist, world, *time_op(
+            torch, lambda: tcu.sharded_full_reduce(local_total), 10))
+        out["C4_full_reduce_2^30_per_gpu_all_gather"] = entry(n30 * world, 2, *ms, world)
+        ms = max_over_ranks(torch, dist, world, *time_op(torch, lambda: tcu.sharded_full_scan(
+            local_total, lambda totals, r: tcu.full_scan(x, out=o, workspace=ws, shard_totals=totals,
+                                                         shard_index=r)), 8))
+        out["C5_full_scan_2^30_per_gpu_f32_all_gather"] = entry(n30 * world, 6, *ms, world)
+    del x, o, ws
+    if world > 1:
+        out["strong_scaling"] = strong_scaling(torch, tcu, dist, args, rank, world, peak_gbs, grp,
+                                               one_gpu, out)
+    grp.close()  # collective
     return out
+
+
+def strong_scaling(torch, tcu, dist, args, rank, world, peak_gbs, grp, one_gpu, weak):
+    """The configurations of the benchmark definition at their STATED totals (2^28 elements for
+    the segmented operations, 2^30 for the full ones) cut into one contiguous shard per GPU.
+    Every output is checked against the fp64 oracle on every rank before it is timed; a
+    mismatch raises.  Shards of this size fit L2, so each timing rotates over enough buffer
+    sets to exceed twice the L2 (segmented legs: one launch per set in a CUDA graph)."""
+    import numpy as np
+    import oracle
+    from tcu_scope_b200.sharded import shard_range
+    dev = torch.device("cuda")
+    res = {}
+    L2_X2 = 2 * 126_000_000
+
+    def bits(t):
+        return t.cpu().view(torch.int16).numpy().view(np.uint16)
+
+    def entry(n_total, bpe, ms_med, ms_min, one_gpu_gelem, **kw):
+        g = n_total / ms_med / 1e6
+        e = {"gelem_per_s": round(g, 1), "gelem_per_s_best": round(n_total / ms_min / 1e6, 1),
+             "hbm_frac_per_gpu": round(g * bpe / peak_gbs / world, 4),
+             "hbm_frac_of_nominal_8tbs_per_gpu": round(g * bpe / NOMINAL_HBM_GBS / world, 4),
+             "ms": round(ms_med, 4), "one_gpu_gelem_per_s": one_gpu_gelem,
+             "x_over_1gpu": round(g / one_gpu_gelem, 3) if one_gpu_gelem else None}
+        e.update(kw)
+        return e
+
+    def all_ok(ok: bool, worst: float):
+        t = torch.tensor([0.0 if ok else 1.0, worst], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if t[0].item() != 0.0:
+            raise AssertionError("a sharded output does not match the fp64 oracle")
+        return float(t[1])
+
+    # ---- C2 / C3: whole segments per rank, no communication
+    n_total = 1 << min(args.log2_elems, 28)
+    SAMPLE = 1 << 18  # elements per checked chunk: the head, the middle and the tail of the shard
+
+    def seg_leg(kind, s, out_dtype):
+        segs = n_total // s
+        sb, se = shard_range(segs, rank, world)
+        n = (se - sb) * s
+        out_elems = (se - sb) if kind == "reduce" else n
+        per_set = n * 2 + out_elems * (4 if out_dtype == torch.float32 else 2)
+        nbuf = max(2, -(-L2_X2 // per_set))
+        xs = [tcu.fill(torch.empty(n, dtype=torch.float16, device=dev), 2024 + i, sb * s) for i in range(nbuf)]
+        os_ = [torch.empty(out_elems, dtype=out_dtype, device=dev) for _ in range(nbuf)]
+
+        def launch(i):
+            if kind == "reduce":
+                tcu.segmented_reduce(xs[i], s, out=os_[i], algo=args.algo)
+            else:
+                tcu.segmented_scan(xs[i], s, out=os_[i], algo=args.algo)
+        launch(0)
+        torch.cuda.synchronize()
+        worst, ok = 0.0, True
+        chunk = max(SAMPLE // s, 1) * s
+        for first in sorted({0, (n // 2) // chunk * chunk, max(n - chunk, 0)}):
+            xb = oracle.c_fill_f16(chunk, 2024, sb * s + first, "uniform_pm1")
+            assert np.array_equal(xb, bits(xs[0][first:first + chunk]))
+            if kind == "reduce":
+                ref = oracle.c_segmented_reduce(xb, s)
+                got = os_[0][first // s:(first + chunk) // s]
+            else:
+                ref = oracle.c_segmented_scan(xb, s)
+                got = os_[0][first:first + chunk]
+            if out_dtype == torch.float32:
+                bad, max_abs, _ = oracle.np_check_f32(got.cpu().numpy(), ref)
+                worst = max(worst, max_abs)
+            else:
+                bad, w = oracle.np_check_f16(bits(got), ref, 2)
+                worst = max(worst, float(w))
+            ok = ok and bad == 0
+        worst = all_ok(ok, worst)
+        ms = max_over_ranks(torch, dist, world, *time_rotating(torch, launch, nbuf, 4))
+        del xs, os_
+        return ms, worst, nbuf
+
+    sweep_ms, sweep_best, worst_all = 0.0, 0.0, 0.0
+    per = {}
+    for s in SWEEP:
+        (ms, best), worst, nbuf = seg_leg("reduce", s, torch.float32)
+        sweep_ms += ms
+        sweep_best += best
+        worst_all = max(worst_all, worst)
+        per[str(s)] = {"ms": round(ms, 4), "gelem_per_s": round(n_total / ms / 1e6, 1),
+                       "hbm_frac_per_gpu": round(n_total * (2 + 4 / s) / ms / 1e6 / peak_gbs / world, 4)}
+    res["C2_seg_reduce_sweep_2^28_total"] = {
+        "gelem_per_s": round(len(SWEEP) * n_total / sweep_ms / 1e6, 1),
+        "one_gpu_gelem_per_s": one_gpu["C2"],
+        "x_over_1gpu": round(len(SWEEP) * n_total / sweep_ms / 1e6 / one_gpu["C2"], 3),
+        "gelem_per_s_best": round(len(SWEEP) * n_total / sweep_best / 1e6, 1),
+        "ms_per_sweep": round(sweep_ms, 4), "per_segment_size": per, "checked": True,
+        "max_abs_err": worst_all, "buffer_sets": nbuf,
+        "timing": "per size: 12 launches per CUDA graph cycling over the buffer sets, max over ranks"}
+    for s, dt, bpe in [(16, torch.float16, 4), (256, torch.float16, 4), (4096, torch.float32, 6)]:
+        (ms, best), worst, nbuf = seg_leg("scan", s, dt)
+        tag = "f32" if dt == torch.float32 else "f16"
+        one_g = weak.get(f"C3_seg_scan_2^28_S{s}_{tag}", {}).get("gelem_per_s")
+        res[f"C3_seg_scan_2^28_total_S{s}_{tag}"] = entry(
+            n_total, bpe, ms, best, one_g, checked=True, buffer_sets=nbuf,
+            **({"max_abs_err": worst} if dt == torch.float32 else {"worst_half_ulp": worst}))
+
+    # ---- C4 / C5: contiguous shards of 2^30 elements in total
+    n_total = 1 << min(args.log2_elems + 2, 30)
+    b, e = shard_range(n_total // 16, rank, world)
+    b, e = b * 16, e * 16
+    n = e - b
+    nbuf = max(1, -(-L2_X2 // (n * 2)))
+    xs = [tcu.fill(torch.empty(n, dtype=torch.float16, device=dev), 3, b, "uniform_01") for _ in range(nbuf)]
+    o = torch.empty(n, dtype=torch.float32, device=dev)
+    o32, o64 = torch.empty(1, dtype=torch.float32, device=dev), torch.empty(1, dtype=torch.float64, device=dev)
+    ws = torch.empty(max(tcu.workspace_bytes(tcu.OP_FULL_SCAN, n, n), tcu.workspace_bytes(tcu.OP_FULL_REDUCE, n, n)),
+                     dtype=torch.uint8, device=dev)
+    k = [0]
+
+    def nxt():
+        k[0] += 1
+        return xs[k[0] % nbuf]
+
+    def local_total(x=None):
+        tcu.full_reduce(xs[k[0] % nbuf] if x is None else x, workspace=ws, out=o32, out_f64=o64)
+        return o64
+
+    # the oracle's view of this shard, block by block: totals of all shards, then the scan
+    BLOCK = 1 << 22
+    run, blocks = 0.0, []
+    for first in range(0, n, BLOCK):
+        m = min(BLOCK, n - first)
+        v = oracle.c_fill_f16(m, 3, b + first, "uniform_01").view(np.float16).astype(np.float64)
+        blocks.append((first, m, run))
+        run += v.sum()
+    t = torch.zeros(world, dtype=torch.float64, device=dev)
+    t[rank] = run
+    dist.all_reduce(t)
+    ref_totals = t.cpu().numpy()
+    ref_total, ref_carry = float(ref_totals.sum()), float(ref_totals[:rank].sum())
+
+    def check_scan(got, label):
+        worst, ok = 0.0, True
+        picks = sorted({0, len(blocks) // 2, len(blocks) - 1})
+        for i in picks:
+            first, m, before = blocks[i]
+            v = oracle.c_fill_f16(m, 3, b + first, "uniform_01").view(np.float16).astype(np.float64)
+            ref = np.cumsum(v) + (ref_carry + before)
+            bad, max_abs, max_rel = oracle.np_check_f32(got[first:first + m].cpu().numpy(), ref)
+            ok = ok and bad == 0
+            worst = max(worst, max_rel)
+        return all_ok(ok, worst)
+
+    # kernel-level exchange
+    grp.full_reduce(xs[0], out=o32, out_f64=o64)
+    torch.cuda.synchronize()
+    err4 = all_ok(abs(float(o64[0]) - ref_total) <= 1e-9 * abs(ref_total), abs(float(o64[0]) - ref_total))
+    grp.full_scan(xs[0], out=o)
+    torch.cuda.synchronize()
+    err5 = check_scan(o, "peer")
+    ms = max_over_ranks(torch, dist, world, *time_op(torch, lambda: grp.full_reduce(nxt(), out=o32, out_f64=o64), 20))
+    res["C4_full_reduce_2^30_total"] = entry(n_total, 2, *ms, one_gpu["C4"], checked=True, abs_err=err4,
+                                             exchange="totals stored by the kernels into every rank's memory",
+                                             buffer_sets=nbuf)
+    ms = max_over_ranks(torch, dist, world, *time_op(torch, lambda: grp.full_scan(nxt(), out=o), 12))
+    res["C5_full_scan_2^30_total_f32"] = entry(n_total, 6, *ms, one_gpu["C5"], checked=True, max_rel_err=err5,
+                                               exchange="totals stored by the kernels into every rank's memory",
+                                               traffic="each shard is read twice: 8 B/elem against 6 algorithmic, "
+                                                       "less what the second read finds in L2",
+                                               buffer_sets=nbuf)
+    # L2 residency of the second read: what the first pass asks L2 to keep
+    sweep = {}
+    for keep_mib in (0, 32, 96):
+        grp.set_l2_keep_bytes(keep_mib << 20)
+        m2 = max_over_ranks(torch, dist, world, *time_op(torch, lambda: grp.full_scan(nxt(), out=o), 8))
+        sweep[f"{keep_mib}MiB"] = round(n_total / m2[0] / 1e6, 1)
+    grp.set_l2_keep_bytes(64 << 20)
+    sweep["64MiB"] = res["C5_full_scan_2^30_total_f32"]["gelem_per_s"]
+    res["C5_full_scan_2^30_total_f32"]["gelem_per_s_by_l2_keep"] = sweep
+
+    # all-gather variant
+    total = tcu.sharded_full_reduce(lambda: local_total(xs[0]))
+    torch.cuda.synchronize()
+    err4 = all_ok(abs(float(total[0]) - ref_total) <= 1e-9 * abs(ref_total), abs(float(total[0]) - ref_total))
+    tcu.sharded_full_scan(lambda: local_total(xs[0]), lambda totals, r: tcu.full_scan(
+        xs[0], out=o, workspace=ws, shard_totals=totals, shard_index=r))
+    torch.cuda.synchronize()
+    err5 = check_scan(o, "all_gather")
+
+    def c4_gather():
+        nxt()
+        tcu.sharded_full_reduce(local_total)
+
+    def c5_gather():
+        x = nxt()
+        tcu.sharded_full_scan(local_total, lambda totals, r: tcu.full_scan(
+            x, out=o, workspace=ws, shard_totals=totals, shard_index=r))
+    ms = max_over_ranks(torch, dist, world, *time_op(torch, c4_gather, 20))
+    res["C4_full_reduce_2^30_total_all_gather"] = entry(n_total, 2, *ms, one_gpu["C4"], checked=True, abs_err=err4)
+    ms = max_over_ranks(torch, dist, world, *time_op(torch, c5_gather, 12))
+    res["C5_full_scan_2^30_total_f32_all_gather"] = entry(n_total, 6, *ms, one_gpu["C5"], checked=True,
+                                                          max_rel_err=err5)
+    return res
 
 
 def reference_kernels_leg(torch, tcu, args):
@@ -515,17 +790,39 @@ def run_e2e(torch, tcu, dist, args, rank, world):
         t = torch.tensor([dt], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t[0])
-    ctx.close()
     h2d = n * 2
     d2h = sum(n // s * 4 for s in SWEEP)
     # spot check: the results that came back are the right ones
     import oracle
     ref = oracle.np_segmented_reduce(h_in[:1 << 20].view(torch.int16).numpy().view(np.uint16), 1024)
     assert np.array_equal(h_out[1024][:1 << 10].numpy(), ref.astype(np.float32))
-    return {"value": steps * len(SWEEP) * n * world / dt / 1e9, "unit": "Gelem/s",
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
-            "note": "tcu_host_segmented_reduce_sweep_f16: pinned host buffers, each 64 MiB chunk "
-                    "copied once and reduced at all six sizes, copies overlap kernels on two streams"}
+    res = {"value": steps * len(SWEEP) * n * world / dt / 1e9, "unit": "Gelem/s",
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
+           "h2d_gbytes_per_s_per_rank": round(steps * h2d / dt / 1e9, 1),
+           "note": "tcu_host_segmented_reduce_sweep_f16: pinned host buffers, each 64 MiB chunk "
+                   "copied once and reduced at all six sizes, copies overlap kernels on two streams"}
+    # What ONE segmented reduction of a host array gets (tcu_host_run_f16): every element crosses
+    # the bus for a single pass, so the call runs at the host-to-device copy rate.
+    single = {}
+    for s in (16, 16384):
+        def one():
+            ctx.run(tcu.OP_SEGMENTED_REDUCE, h_in, h_out[s], s, algo=args.algo)
+        one()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(2):
+            one()
+        d1 = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([d1], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            d1 = float(t[0])
+        single[str(s)] = {"gelem_per_s": round(2 * n * world / d1 / 1e9, 2),
+                          "h2d_gbytes_per_s_per_rank": round(2 * h2d / d1 / 1e9, 1)}
+    res["single_size_calls"] = single
+    ctx.close()
+    return res
 
 
 def profile_pass(torch, tcu, args, n, json_fd):
@@ -675,16 +972,19 @@ def _main(args, json_fd):
         bpe = 2 + 4 / s
         per_size[str(s)] = {"ms": round(ms, 4), "gelem_per_s": round(n / ms / 1e6, 1),
                             "gbytes_per_s": round(n * bpe / ms / 1e6, 1),
-                            "hbm_frac": round(n * bpe / ms / 1e6 / peak_gbs, 4)}
+                            "hbm_frac": round(n * bpe / ms / 1e6 / peak_gbs, 4),
+                            "hbm_frac_of_nominal_8tbs": round(n * bpe / ms / 1e6 / NOMINAL_HBM_GBS, 4)}
 
     # dominant kernel: the 16-element launch moves the most bytes (2 + 4/16 per element)
     dom = per_size["16"]
+    traffic, traffic_source = ncu_traffic(n)
     roofline = {"bound": "hbm", "kernel": "seg_reduce_kernel<4> (segment size 16)",
                 "achieved": dom["gbytes_per_s"], "peak": peak_gbs, "unit": "GB/s",
                 "frac": dom["hbm_frac"], "peak_source": f"of {peak_kind}",
+                "frac_of_nominal_8tbs": dom["hbm_frac_of_nominal_8tbs"],
                 "algorithmic_bytes_per_launch": int(n * 2.25),
                 "timing": "back-to-back launches of this kernel (6 per graph replay), CUDA events",
-                "traffic": NCU_TRAFFIC_BYTES_S16 if args.log2_elems == 28 else None}
+                "traffic": traffic, "traffic_source": traffic_source}
 
     result = {
         "metric": "segmented_reduce_sweep_throughput", "value": round(value, 2), "unit": "Gelem/s",
@@ -697,7 +997,7 @@ def _main(args, json_fd):
 
     if not args.no_extras:
         result["e2e"] = run_e2e(torch, tcu, dist, args, rank, world)
-        result["other_configs"] = extras(torch, tcu, dist, args, rank, world, peak_gbs)
+        result["other_configs"] = extras(torch, tcu, dist, args, rank, world, peak_gbs, value / world)
         if rank == 0 and world == 1:
             v, cores, passes, secs = cpu_sweep(26, 8.0, 2000)
             result["cpu_baseline"] = {

@@ -240,10 +240,83 @@ int tcu_host_segmented_reduce_sweep_f16(tcu_host_ctx* ctx, const void* h_in, siz
                                         int num_sizes, const size_t* segment_sizes,
                                         void* const* h_outs, int out_type, int algo);
 
+/*
+ * Full reduction and full scan of ONE array sharded contiguously over the GPUs
+ * of a node: rank r holds elements [begin_r, end_r) in its own device memory
+ * and keeps its part of the output.  The reference is single-device
+ * (src/init/cuda.cpp:45 selects one GPU and nothing in src/ talks to another),
+ * so these entry points have no counterpart there; they are what its full
+ * operations (src/reduction/wmma_2kers.cu:65-81, src/prefixsum/wmma_3kers.cu:63-70)
+ * become when the array does not live on one GPU.
+ *
+ * One context per GPU.  The GPUs exchange one double each per call -- the
+ * shard totals -- which the reduction kernel's last thread block stores
+ * straight into a small slot array in every rank's memory; the scan kernel of
+ * rank r waits (bounded) for the totals of ranks < r in its own memory.  No
+ * library collective runs per call.  Set-up:
+ *   - one process per GPU: every rank calls tcu_mgpu_ctx_create, which fills
+ *     handle_out (TCU_MGPU_HANDLE_BYTES bytes, a CUDA IPC handle of its slot
+ *     array); the ranks exchange the handles by any means they have (one
+ *     all-gather at start-up) and pass all of them, in rank order, to
+ *     tcu_mgpu_ctx_connect;
+ *   - one process driving several devices: create one context per device (with
+ *     that device current; handle_out may be NULL) and call
+ *     tcu_mgpu_ctx_connect_local on each with the array of all contexts.
+ * Rules: every rank makes the same sequence of tcu_mgpu_full_* calls, each on
+ * one stream of its own GPU, and the calls of one context do not overlap;
+ * a rank whose peers never make the matching call gives up after about two
+ * seconds and reports TCU_ERR_TIMEOUT through tcu_device_error (bit 2).
+ * Destroy a context only after EVERY rank has finished its last call
+ * (synchronise, then meet at a host barrier): peers store into its memory.
+ *
+ * tcu_mgpu_full_reduce_f16: *d_out (and *d_out_f64 if not NULL) receive the
+ * sum over all ranks' shards, on every rank.
+ * tcu_mgpu_full_scan_f16: d_out[i] = (sum of all earlier ranks' shards) +
+ * in[0] + ... + in[i]; two passes over the shard (reduce, then scan).
+ * num_elements: this rank's shard, a multiple of 16, may be 0.
+ * tcu_mgpu_ctx_set_l2_keep_bytes: how much of the shard the first pass asks
+ * L2 to keep for the second (default 64 MiB; 0 = nothing).
+ */
+#define TCU_MGPU_HANDLE_BYTES 64
+#define TCU_MGPU_MAX_RANKS 16
+typedef struct tcu_mgpu_ctx tcu_mgpu_ctx;
+int tcu_mgpu_ctx_create(tcu_mgpu_ctx** ctx, int rank, int world, void* handle_out);
+int tcu_mgpu_ctx_connect(tcu_mgpu_ctx* ctx, const void* handles);
+int tcu_mgpu_ctx_connect_local(tcu_mgpu_ctx* ctx, tcu_mgpu_ctx* const* group);
+int tcu_mgpu_ctx_set_l2_keep_bytes(tcu_mgpu_ctx* ctx, size_t bytes);
+void tcu_mgpu_ctx_destroy(tcu_mgpu_ctx* ctx);
+int tcu_mgpu_full_reduce_f16(tcu_mgpu_ctx* ctx, const void* d_in, float* d_out, double* d_out_f64,
+                             size_t num_elements, void* stream);
+int tcu_mgpu_full_scan_f16(tcu_mgpu_ctx* ctx, const void* d_in, void* d_out, int out_type,
+                           size_t num_elements, void* stream);
+
 /* Reads (and optionally clears) the device-side error word of the current
  * device: bit 0 = an mbarrier wait ran out, bit 1 = a tile-status poll ran
- * out.  Synchronises the device.  Returns TCU_ERR_TIMEOUT if any bit is set. */
+ * out, bit 2 = a wait for another GPU's total ran out.  Synchronises the
+ * device.  Returns TCU_ERR_TIMEOUT if any bit is set. */
 int tcu_device_error(unsigned int* bits, int clear);
+
+/*
+ * Test hooks for the bounded waits (the reference has none: its one
+ * device-side spin barrier is disabled as a dead lock,
+ * src/prefixsum/wmma_atomic.cu:189).  Every device-side wait of the library
+ * gives up after a limit and raises a bit of the error word instead of
+ * hanging; these two calls let a test see that happen within a millisecond.
+ * tcu_test_set_wait_limits: attempts before an mbarrier wait, a tile-status
+ * poll, a shared-memory flag poll and a peer-total poll give up, on the
+ * current device; 0 restores that limit's default.
+ * tcu_test_inject: arms ONE stall for the next matching call on this host
+ * thread's library state -- TCU_TEST_SKIP_TILE_LOAD: the next segmented or
+ * full reduction never loads tile `arg` of CTA 0's tiles (its consumers'
+ * barrier is never armed); TCU_TEST_LOOKBACK_TICKET: the next look-back scan
+ * hands out tiles starting at `arg` instead of 0 (tile `arg` polls status
+ * words nobody publishes).  Nothing faults or traps: the waits run out, the
+ * kernels return, the outputs of that call are wrong and flagged.
+ */
+typedef enum { TCU_TEST_NONE = 0, TCU_TEST_SKIP_TILE_LOAD = 1, TCU_TEST_LOOKBACK_TICKET = 2 } tcu_test_stall;
+int tcu_test_set_wait_limits(unsigned barrier_attempts, unsigned status_polls, unsigned flag_polls,
+                             unsigned peer_polls);
+int tcu_test_inject(int what, unsigned long long arg);
 
 /* Geometry the kernels were built with, for callers that size experiments. */
 int tcu_tile_elements(void);

@@ -11,14 +11,14 @@ _lib.load()
 
 from .ops import (  # noqa: E402
     ALGO, DIST, OP_FULL_REDUCE, OP_FULL_SCAN, OP_SEGMENTED_REDUCE, OP_SEGMENTED_SCAN,
-    HostContext, TcuError, device_error, fill, full_reduce, full_scan, segmented_reduce,
+    HostContext, TcuError, device_error, fill, full_reduce, full_scan, num_sms, segmented_reduce,
     segmented_scan, workspace_bytes,
 )
-from .sharded import sharded_full_reduce, sharded_full_scan, shard_range  # noqa: E402
+from .sharded import PeerGroup, sharded_full_reduce, sharded_full_scan, shard_range  # noqa: E402
 
 __all__ = [
     "ALGO", "DIST", "OP_FULL_REDUCE", "OP_FULL_SCAN", "OP_SEGMENTED_REDUCE", "OP_SEGMENTED_SCAN",
-    "HostContext", "TcuError", "device_error", "fill", "full_reduce", "full_scan",
+    "HostContext", "TcuError", "device_error", "fill", "full_reduce", "full_scan", "num_sms",
     "segmented_reduce", "segmented_scan", "workspace_bytes", "sharded_full_reduce",
-    "sharded_full_scan", "shard_range",
+    "sharded_full_scan", "shard_range", "PeerGroup",
 ]

@@ -9,9 +9,7 @@ import ctypes
 import os
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-# TCU_SCOPE_LIB selects another build of the same library (e.g. one compiled with
-# different tuning macros); the default is the in-tree build.
-LIB_PATH = os.environ.get("TCU_SCOPE_LIB") or os.path.join(PKG_DIR, "libtcu_scope.so")
+LIB_PATH = os.path.join(PKG_DIR, "libtcu_scope.so")
 
 c_size_t, c_int, c_void_p = ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p
 
@@ -55,7 +53,16 @@ SIGNATURES = {
     "tcu_host_segmented_reduce_sweep_f16": (c_int, [c_void_p, c_void_p, c_size_t, c_int,
                                                     ctypes.POINTER(c_size_t),
                                                     ctypes.POINTER(c_void_p), c_int, c_int]),
+    "tcu_mgpu_ctx_create": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
+    "tcu_mgpu_ctx_connect": (c_int, [c_void_p, c_void_p]),
+    "tcu_mgpu_ctx_connect_local": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "tcu_mgpu_ctx_set_l2_keep_bytes": (c_int, [c_void_p, c_size_t]),
+    "tcu_mgpu_ctx_destroy": (None, [c_void_p]),
+    "tcu_mgpu_full_reduce_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "tcu_mgpu_full_scan_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p]),
     "tcu_device_error": (c_int, [ctypes.POINTER(ctypes.c_uint), c_int]),
+    "tcu_test_set_wait_limits": (c_int, [ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "tcu_test_inject": (c_int, [c_int, ctypes.c_ulonglong]),
     "tcu_tile_elements": (c_int, []),
     "tcu_num_sms": (c_int, []),
     "tcu_status_string": (ctypes.c_char_p, [c_int]),

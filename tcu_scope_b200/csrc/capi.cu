@@ -18,6 +18,9 @@
 #include "scan_lookback_kernel.cuh"
 #include "shuffle_kernels.cuh"
 #include "tcgen05_reduce_kernel.cuh"
+#if !TCU_BF16
+#include "shard_kernels.cuh"
+#endif
 
 #if TCU_BF16
 // Second compilation of this file (capi_bf16.cu): the same entry points for
@@ -49,13 +52,26 @@ int g_sm_count[kMaxDevices];
 // lives in every GPU's memory from the moment the library is loaded there.
 // In host code the name below is only a handle for the runtime, never a device
 // address: the address is looked up once per device with cudaGetSymbolAddress.
+// Workspace of the look-back scan: header | one status word per tile | one per
+// block of 32 tiles (+1 per segment for a partial last block; a segment has at
+// least 2 tiles, so tiles/2 bounds it).
+constexpr size_t scan_long_ws_bytes_for_tiles(size_t tiles) {
+  return kWsHeader + tiles * 8 + (tiles / 32 + tiles / 2 + 2) * 8;
+}
 #if !TCU_BF16
 constexpr size_t kStaticScanMaxElems = size_t(1) << 30;
 constexpr size_t kStaticScanMaxTiles = kStaticScanMaxElems / kTileElems;
-constexpr size_t kStaticScratchBytes =
-    kWsHeader + kStaticScanMaxTiles * 8 + (kStaticScanMaxTiles / 32 + kStaticScanMaxTiles / 2 + 2) * 8;
+constexpr size_t kStaticScratchBytes = scan_long_ws_bytes_for_tiles(kStaticScanMaxTiles);
+static_assert(kStaticScanMaxElems == TCU_STATIC_SCAN_MAX_ELEMENTS &&
+                  kStaticScanMaxTiles == TCU_STATIC_SCAN_MAX_TILES &&
+                  kStaticScratchBytes == TCU_STATIC_SCAN_SCRATCH_BYTES,
+              "include/tcu_scope.h states another size for the built-in scratch");
 static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScratchBytes];
 void* g_static_scan_scratch_addr[kMaxDevices];  // device address, per device; null = not looked up
+
+// One-shot stalls armed by tcu_test_inject() for the next matching call.
+unsigned long long g_test_skip_tile   = ~0ull;
+unsigned long long g_test_ticket_from = 0;
 #endif
 
 int current_device() {
@@ -162,8 +178,8 @@ cudaError_t launch_scan(const ScanParams& p, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
   cudaError_t e = ensure_smem(seg_scan_kernel<SC, OUT32>, configured, scan_dyn_smem_bytes(SC));
   if (e != cudaSuccess) return e;
-  return launch_pdl(seg_scan_kernel<SC, OUT32>, p, grid * scan_ctas_per_sm(SC), kThreads,
-                    scan_dyn_smem_bytes(SC), st);
+  return launch_pdl(seg_scan_kernel<SC, OUT32>, p, grid * scan_ctas_per_sm(SC),
+                    SliceShape<scan_warps(SC, OUT32)>::kThreads, scan_dyn_smem_bytes(SC), st);
 }
 
 // cuTensorMapEncodeTiled, looked up once through the runtime (no link against libcuda).
@@ -248,13 +264,10 @@ cudaError_t launch_shuffle_scan(const ScanParams& p, int grid, cudaStream_t st) 
 
 size_t reduce_long_ws_bytes() { return kWsHeader + size_t(2) * kMaxLongGrid * 16; }
 
-// header | one status word per tile | one per block of 32 tiles (+1 per segment
-// for a partial last block; a segment has at least 2 tiles, so tiles/2 bounds it)
 size_t scan_long_tiles(size_t num_elements) { return (num_elements + kTileElems - 1) / kTileElems; }
 
 size_t scan_long_ws_bytes(size_t num_elements) {
-  const size_t tiles = scan_long_tiles(num_elements);
-  return kWsHeader + tiles * 8 + (tiles / 32 + tiles / 2 + 2) * 8;
+  return scan_long_ws_bytes_for_tiles(scan_long_tiles(num_elements));
 }
 
 int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
@@ -286,6 +299,11 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   p.num_segments = num_segments;
   p.out_is_f32   = out_type == TCU_OUT_F32;
   p.out_f64      = d_out_f64;
+  p.test_skip_tile = ~0ull;
+#if !TCU_BF16
+  p.test_skip_tile = g_test_skip_tile;  // one-shot stall armed by a test, see tcu_test_inject
+  g_test_skip_tile = ~0ull;
+#endif
   const size_t tiles = (n + kTileElems - 1) / kTileElems;
   int grid           = tiles < size_t(sms) ? int(tiles) : sms;
 
@@ -388,6 +406,12 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
     p.shard_totals      = shard_totals;
     p.shard_index       = shard_index;
     if (cudaMemsetAsync(w, 0, need, st) != cudaSuccess) return TCU_ERR_CUDA;
+#if !TCU_BF16
+    if (g_test_ticket_from != 0) {  // one-shot stall armed by a test: tiles below it are never scanned
+      if (cudaMemsetAsync(w, int(g_test_ticket_from & 0xffu), 1, st) != cudaSuccess) return TCU_ERR_CUDA;
+      g_test_ticket_from = 0;
+    }
+#endif
     const size_t want = size_t(sms) * kLookbackCtasPerSm;
     const int lgrid   = tiles < want ? int(tiles) : int(want);
     if (algo == TCU_ALGO_SHUFFLE) return TCU_ERR_UNSUPPORTED;
@@ -506,10 +530,10 @@ int tcu_full_scan_f16_static(const void* d_in, void* d_out, int out_type, size_t
 size_t tcu_workspace_bytes(int op, size_t num_elements, size_t segment_size) {
   switch (op) {
     case TCU_OP_SEGMENTED_REDUCE:
-      return segment_size > size_t(kTileElems) ? reduce_long_ws_bytes() : 0;
+      return segment_class(segment_size) == kClassLong ? reduce_long_ws_bytes() : 0;
     case TCU_OP_FULL_REDUCE: return reduce_long_ws_bytes();
     case TCU_OP_SEGMENTED_SCAN:
-      return segment_size > size_t(kTileElems) ? scan_long_ws_bytes(num_elements) : 0;
+      return segment_class(segment_size) == kClassLong ? scan_long_ws_bytes(num_elements) : 0;
     case TCU_OP_FULL_SCAN: return scan_long_ws_bytes(num_elements);
     default: return 0;
   }
@@ -554,6 +578,25 @@ int tcu_error_word_of_this_build(unsigned int* bits, int clear) {
   return TCU_OK;
 }
 
+// Likewise for the wait limits of the build this is compiled in (0 = default).
+#if TCU_BF16
+#define tcu_wait_limits_of_this_build tcu_wait_limits_bf16_build
+#else
+#define tcu_wait_limits_of_this_build tcu_wait_limits_f16_build
+#endif
+int tcu_wait_limits_f16_build(const unsigned int* four);
+int tcu_wait_limits_bf16_build(const unsigned int* four);
+
+int tcu_wait_limits_of_this_build(const unsigned int* four) {
+  WaitLimits w = kDefaultWaitLimits;
+  if (four[0]) w.barrier = four[0];
+  if (four[1]) w.status = four[1];
+  if (four[2]) w.flag = four[2];
+  if (four[3]) w.peer = four[3];
+  if (cudaDeviceSynchronize() != cudaSuccess) return TCU_ERR_CUDA;
+  return cudaMemcpyToSymbol(g_wait_limits, &w, sizeof(w)) == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+}
+
 #if !TCU_BF16
 int tcu_device_error(unsigned int* bits, int clear) {
   unsigned int a = 0, b = 0;
@@ -563,18 +606,27 @@ int tcu_device_error(unsigned int* bits, int clear) {
   return (a | b) ? TCU_ERR_TIMEOUT : TCU_OK;
 }
 
-#ifdef TCU_LB_PROFILE
-// debug build only: look-back timing counters (see scan_lookback_kernel.cuh)
-int tcu_debug_lookback_stats(unsigned long long* out8, int clear) {
-  cudaDeviceSynchronize();
-  if (cudaMemcpyFromSymbol(out8, g_lb_stats, 128) != cudaSuccess) return TCU_ERR_CUDA;
-  if (clear) {
-    unsigned long long z[16] = {0};
-    cudaMemcpyToSymbol(g_lb_stats, z, 128);
-  }
-  return TCU_OK;
+int tcu_test_set_wait_limits(unsigned barrier_attempts, unsigned status_polls, unsigned flag_polls,
+                             unsigned peer_polls) {
+  const unsigned int four[4] = {barrier_attempts, status_polls, flag_polls, peer_polls};
+  if (tcu_wait_limits_f16_build(four) != TCU_OK) return TCU_ERR_CUDA;
+  return tcu_wait_limits_bf16_build(four);
 }
-#endif
+
+int tcu_test_inject(int what, unsigned long long arg) {
+  switch (what) {
+    case TCU_TEST_NONE:
+      g_test_skip_tile   = ~0ull;
+      g_test_ticket_from = 0;
+      return TCU_OK;
+    case TCU_TEST_SKIP_TILE_LOAD: g_test_skip_tile = arg; return TCU_OK;
+    case TCU_TEST_LOOKBACK_TICKET:
+      if (arg == 0 || arg > 255) return TCU_ERR_INVALID_ARG;
+      g_test_ticket_from = arg;
+      return TCU_OK;
+    default: return TCU_ERR_UNSUPPORTED;
+  }
+}
 
 int tcu_tile_elements(void) { return kTileElems; }
 
@@ -599,4 +651,5 @@ const char* tcu_status_string(int status) {
 
 #if !TCU_BF16
 #include "host_pipeline.inl"
+#include "mgpu.inl"
 #endif

@@ -32,29 +32,38 @@ namespace TCU_NS {
 // ---------------------------------------------------------------- geometry
 // One CTA tile is what a single TMA bulk copy brings into one ring stage.  A
 // tile is cut into one contiguous slice per consumer warp.
-#ifndef TCU_STAGES
-#define TCU_STAGES 4
-#endif
 constexpr int kConsumerWarps = 8;
 constexpr int kSliceElems    = 2048;                         // halves per warp slice
 constexpr int kSliceBytes    = kSliceElems * 2;              // 4 KiB
 constexpr int kTileElems     = kSliceElems * kConsumerWarps; // 16384 halves per tile
 constexpr int kTileBytes     = kTileElems * 2;               // 32 KiB
-constexpr int kStages        = TCU_STAGES;                   // 4 stages = 128 KiB in flight per SM
+constexpr int kStages        = 4;                            // 4 stages = 128 KiB in flight per SM
 constexpr int kThreads       = (kConsumerWarps + 1) * 32;    // + 1 producer warp
 constexpr int kRingBytes     = kStages * kTileBytes;
 
 // Device-side error word bits (read back by tcu_device_error()).
 constexpr unsigned kErrBarrierTimeout  = 1u;  // an mbarrier wait ran out
 constexpr unsigned kErrLookbackTimeout = 2u;  // a tile-status poll ran out
+constexpr unsigned kErrPeerTimeout     = 4u;  // a wait for another GPU's total ran out
 
 // Wait bounds.  try_wait suspends for at most kWaitHintNs per attempt, so a
-// wait gives up after roughly kWaitAttempts * kWaitHintNs (about 2 s) instead
-// of hanging the device.
-constexpr uint32_t kWaitHintNs   = 1000;
-constexpr uint32_t kWaitAttempts = 1u << 21;
-constexpr uint32_t kPollAttempts = 1u << 22;  // tile-status polls (each ~0.5 us)
-constexpr uint32_t kSpinAttempts = 1u << 24;  // shared-memory flag polls between warps of a CTA
+// wait gives up after roughly barrier * kWaitHintNs (about 2 s) instead of
+// hanging the device.  The limits live in device memory so that a test can
+// shorten them and make a wait run out within a millisecond; a kernel reads
+// them only after a first attempt has failed, never on its fast path.
+constexpr uint32_t kWaitHintNs = 1000;
+struct WaitLimits {
+  uint32_t barrier;  // mbarrier try_wait attempts
+  uint32_t status;   // tile-status polls of the look-back (each ~0.5 us)
+  uint32_t flag;     // shared-memory flag polls between warps of a CTA
+  uint32_t peer;     // polls of a total another GPU stores into this one's memory (each ~0.5 us)
+};
+constexpr WaitLimits kDefaultWaitLimits = {1u << 21, 1u << 22, 1u << 24, 1u << 23};
+__device__ WaitLimits g_wait_limits = kDefaultWaitLimits;
+
+__device__ __forceinline__ uint32_t wait_limit(const uint32_t* field) {
+  return *reinterpret_cast<const volatile uint32_t*>(field);
+}
 
 __device__ unsigned int g_error_word;  // sticky until cleared by the host
 
@@ -85,7 +94,8 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 // Bounded wait on a phase parity.  Returns false (after raising the error
 // word) when the phase never completed.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t attempt = 0; attempt < kWaitAttempts; ++attempt) {
+  uint32_t limit = 1;  // the real bound is fetched once a first attempt has failed
+  for (uint32_t attempt = 0; attempt < limit; ++attempt) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -95,6 +105,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     if (done) return true;
+    if (attempt == 0) limit = wait_limit(&g_wait_limits.barrier);
   }
   raise_error(kErrBarrierTimeout);
   return false;
@@ -218,8 +229,9 @@ __device__ __forceinline__ uint2 lds64(const uint8_t* p) {
 // Zero the tail [valid_bytes, kSliceBytes) of one warp's slice.  Only the last
 // tile of an array can be short; stale shared memory behind it may hold NaN or
 // Inf bit patterns, and 0 * NaN inside the contraction would poison valid rows.
+template <int kBytes = kSliceBytes>
 __device__ __forceinline__ void zero_slice_tail(uint8_t* slice, int valid_bytes, int lane) {
-  for (int b = valid_bytes + lane * 16; b < kSliceBytes; b += 32 * 16)
+  for (int b = valid_bytes + lane * 16; b < kBytes; b += 32 * 16)
     *reinterpret_cast<uint4*>(slice + b) = make_uint4(0u, 0u, 0u, 0u);
   __syncwarp();
 }

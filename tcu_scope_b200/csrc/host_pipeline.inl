@@ -177,16 +177,24 @@ int tcu_host_segmented_reduce_sweep_f16(tcu_host_ctx* c, const void* h_in, size_
     return TCU_ERR_INVALID_ARG;
   if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
   if (num_elements == 0) return TCU_OK;
-  size_t max_seg = 0;
+  // every chunk must hold whole segments of EVERY size: a multiple of their least common
+  // multiple (for the powers of two of the reference's sweep that is the largest size)
+  size_t unit = 1;
   for (int i = 0; i < num_sizes; ++i) {
     if (!h_outs[i]) return TCU_ERR_INVALID_ARG;
     if (segment_class(segment_sizes[i]) < 0) return TCU_ERR_UNSUPPORTED;
     if (num_elements % segment_sizes[i] != 0) return TCU_ERR_INVALID_ARG;
-    if (segment_sizes[i] > max_seg) max_seg = segment_sizes[i];
+    size_t a = unit, b = segment_sizes[i];
+    while (b != 0) {
+      const size_t r = a % b;
+      a = b;
+      b = r;
+    }
+    const size_t step = segment_sizes[i] / a;  // unit * step = lcm(unit, size)
+    if (step > c->chunk_elems / unit) return TCU_ERR_UNSUPPORTED;  // no chunk holds whole segments of all sizes
+    unit *= step;
   }
-  if (max_seg > c->chunk_elems) return TCU_ERR_UNSUPPORTED;
-  // sizes are powers of two: a multiple of the largest is a multiple of all
-  const size_t chunk    = c->chunk_elems / max_seg * max_seg;
+  const size_t chunk    = c->chunk_elems / unit * unit;
   const size_t out_elem = out_type == TCU_OUT_F32 ? 4 : 2;
   // all outputs of one chunk share the staging buffer (chunk * 4 bytes): with every
   // size >= 16 and at most 32 sizes they need at most 32 * chunk/16 * 4 bytes -- check anyway

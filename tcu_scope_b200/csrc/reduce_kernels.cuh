@@ -33,6 +33,7 @@ struct ReduceParams {
   long long* bound_seg;                  // [2 * gridDim.x] their segment, -1 = none
   unsigned int* done_counter;            // zeroed by the host before the launch
   double* out_f64;                       // optional: segment sums in double (may be null)
+  unsigned long long test_skip_tile;     // ~0 in production; a test names a tile that is never loaded
 };
 
 // Segment classes.  4..11: segment_size = 2^class, whole segments inside one
@@ -278,6 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
         const unsigned long long off = tile * kTileBytes;
         const unsigned long long rem = total_bytes - off;
         const uint32_t bytes = rem < (unsigned long long)kTileBytes ? (uint32_t)rem : kTileBytes;
+        if (tile == p.test_skip_tile) continue;  // test hook: this stage's barrier is never armed
         mbar_arrive_expect_tx(full0 + 8 * s, bytes);
         tma_load_1d(ring_u32 + s * kTileBytes, p.in + off, bytes, full0 + 8 * s);
       }

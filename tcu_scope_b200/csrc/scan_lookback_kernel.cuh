@@ -33,25 +33,12 @@
 
 namespace TCU_NS {
 
-#ifndef TCU_LB_STREAM_STORES
-#define TCU_LB_STREAM_STORES 1
-#endif
-#ifndef TCU_LB_RING_A
-#define TCU_LB_RING_A 2
-#endif
-#ifndef TCU_LB_RING_B
-#define TCU_LB_RING_B 3
-#endif
-#ifndef TCU_LB_QUEUE
-#define TCU_LB_QUEUE 10
-#endif
-constexpr int kRingA = TCU_LB_RING_A;  // stages of the first-read ring
-constexpr int kRingB = TCU_LB_RING_B;  // stages of the second-read ring
-constexpr int kQueue = TCU_LB_QUEUE;   // tiles between their first and second read, per CTA
-#ifndef TCU_LB_WARPS
-#define TCU_LB_WARPS 6
-#endif
-constexpr int kLookbackWarps        = TCU_LB_WARPS;
+// Ring and queue depths are measured optima (sweep at 2^30 elements): rings of
+// 2 + 3 stages and 10 queue slots; 6 look-back warps keep up with the tiles.
+constexpr int kRingA = 2;   // stages of the first-read ring
+constexpr int kRingB = 3;   // stages of the second-read ring
+constexpr int kQueue = 10;  // tiles between their first and second read, per CTA
+constexpr int kLookbackWarps = 6;
 // A look-back warp's first tile must be in the first pass over the queue: a
 // wait for a later phase on a fresh barrier would fall through.
 static_assert(kLookbackWarps <= kQueue, "at most one look-back warp per queue slot");
@@ -62,35 +49,14 @@ constexpr int kProducerAWarp        = 2 * kConsumerWarps;
 constexpr int kProducerBWarp        = kProducerAWarp + 1;
 constexpr int kLookbackWarp0        = kProducerBWarp + 1;
 constexpr int kLookbackThreads      = (2 * kConsumerWarps + 2 + kLookbackWarps) * 32;
-#ifndef TCU_LB_SAVE_CARRIES
-#define TCU_LB_SAVE_CARRIES 1
-#endif
-// one float4 (row carries) per pass-1 lane, kept from pass 1 to pass 2 -- or
-// nothing, and pass 2 sums the rows of its slice again
-constexpr bool kSaveCarries         = TCU_LB_SAVE_CARRIES != 0;
+// one float4 (row carries) per pass-1 lane, kept from pass 1 to pass 2 (summing
+// the rows of the slice again in pass 2 instead measured 0.55 against 0.88)
+constexpr bool kSaveCarries         = true;
 constexpr int kCarryBytesPerSlot    = kSaveCarries ? kConsumerWarps * 32 * 16 : 0;
 constexpr int kLookbackDynSmemBytes =
     (kRingA + kRingB) * kTileBytes + kQueue * kCarryBytesPerSlot + 1024;
 constexpr uint32_t kNoEnd = 0xffffffffu;
 
-#ifdef TCU_LB_PROFILE
-// debug counters (ns): [0] look-back time sum [1] tiles [2] look-back max
-// [3] pass-2 warp 8 wait for resolved  [4] pass-1 warp 0 wait for full  [5] pass-1 compute
-// [6] pass-2 compute  [7] producer wait for empty
-// [8] in-block walk ns [9] block walk ns [10] in-block empty polls [11] block empty polls
-// [12] ns from the tile's ticket to the start of its look-back
-__device__ unsigned long long g_lb_stats[16];
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define LB_T0() const unsigned long long lb_t0 = gtime()
-#define LB_ADD(slot, cond) do { if (cond) atomicAdd(&g_lb_stats[slot], gtime() - lb_t0); } while (0)
-#else
-#define LB_T0()
-#define LB_ADD(slot, cond)
-#endif
 constexpr unsigned long long kTileEnd = ~0ull;
 constexpr unsigned kStateAggregate = 1u, kStateInclusive = 2u;
 constexpr unsigned long long kBlockTiles = 32;  // tiles per second-level status word
@@ -124,9 +90,6 @@ __device__ __forceinline__ double look_back(const unsigned long long* status, lo
   double sum     = 0.0;
   uint32_t polls = 0;
   found_inclusive = false;
-#ifdef TCU_LB_PROFILE
-  const bool use_prefetched_slot = use_prefetched;  // block-level walks are the prefetched ones
-#endif
   while (last >= first) {
     const long long idx = last - lane;
     const bool valid    = idx >= first;
@@ -151,10 +114,7 @@ __device__ __forceinline__ double look_back(const unsigned long long* status, lo
     }
     last -= take;
     if (take == 0) {  // the nearest word is still empty: wait for its tile, but not forever
-#ifdef TCU_LB_PROFILE
-      if (lane == 0) atomicAdd(&g_lb_stats[status == nullptr ? 10 : 10 + (int)use_prefetched_slot], 1ull);
-#endif
-      if (++polls > kPollAttempts) {
+      if (++polls > wait_limit(&g_wait_limits.status)) {
         if (lane == 0) raise_error(kErrLookbackTimeout);
         return sum;  // wrong result, flagged, but no hang
       }
@@ -169,7 +129,8 @@ __device__ __forceinline__ double look_back(const unsigned long long* status, lo
 __device__ __forceinline__ bool mbar_wait_or_stop(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag,
                                                   volatile uint32_t* end_index, uint32_t idx) {
-  for (uint32_t attempt = 0; attempt < kWaitAttempts; ++attempt) {
+  uint32_t limit = 1;  // the real bound is fetched once a first attempt has failed
+  for (uint32_t attempt = 0; attempt < limit; ++attempt) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -179,6 +140,7 @@ __device__ __forceinline__ bool mbar_wait_or_stop(uint32_t bar, uint32_t parity,
         : "r"(bar), "r"(parity), "r"(kWaitHintNs)
         : "memory");
     if (done) return true;
+    if (attempt == 0) limit = wait_limit(&g_wait_limits.barrier);
     if (*abort_flag) return false;
     if (end_index != nullptr && *end_index <= idx) return false;
   }
@@ -261,12 +223,8 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       const uint64_t keep = l2_policy_evict_last();  // the tile is read again within microseconds
       for (uint32_t i = 0;; ++i) {
         const uint32_t a = i % NA, q = i % NQ;
-        {
-          LB_T0();
-          if (!mbar_wait_or_stop(qfree0 + 8 * q, ((i / NQ) & 1u) ^ 1u, abort_flag, nullptr, 0)) break;
-          if (!mbar_wait_or_stop(empty_a0 + 8 * a, ((i / NA) & 1u) ^ 1u, abort_flag, nullptr, 0)) break;
-          LB_ADD(7, true);
-        }
+        if (!mbar_wait_or_stop(qfree0 + 8 * q, ((i / NQ) & 1u) ^ 1u, abort_flag, nullptr, 0)) break;
+        if (!mbar_wait_or_stop(empty_a0 + 8 * a, ((i / NA) & 1u) ^ 1u, abort_flag, nullptr, 0)) break;
         const unsigned long long tile = atomicAdd(p.ticket, 1u);
         if (tile >= num_tiles) {
           slot_tile[q] = kTileEnd;
@@ -300,7 +258,6 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       const uint32_t q = i % NQ, ph = (i / NQ) & 1u;
       if (!mbar_wait_or_stop(p1done0 + 8 * q, ph, abort_flag, end_index, i)) break;
       const unsigned long long tile = slot_tile[q];
-      LB_T0();
       double agg = 0.0;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) agg += (double)part[q][w].x + (double)part[q][w].y;
@@ -331,10 +288,6 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
         bool complete = false;
         const double in_block = look_back(p.tile_status, (long long)tile - 1,
                                           (long long)blk_first, lane, complete);
-#ifdef TCU_LB_PROFILE
-        const unsigned long long lb_t1 = gtime();
-        if (lane == 0) atomicAdd(&g_lb_stats[8], lb_t1 - lb_t0);
-#endif
         double before_block = 0.0;
         if (!complete) {  // blk > 0 here: block 0 starts with the segment's inclusive first tile
           if (closes_block && lane == 0)
@@ -344,9 +297,6 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
                                    /*use_prefetched=*/true, blk_word);
         }
         excl = before_block + in_block;
-#ifdef TCU_LB_PROFILE
-        if (lane == 0) atomicAdd(&g_lb_stats[9], gtime() - lb_t1);
-#endif
         if (lane == 0) status_store(p.tile_status + tile, excl + agg, kStateInclusive);
       }
       // the last tile of a block publishes the prefix through the block
@@ -355,12 +305,6 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       if (lane == 0) {
         tile_excl[q] = excl;
         mbar_arrive(resolved0 + 8 * q);  // release: tile_excl is visible to the waiters
-#ifdef TCU_LB_PROFILE
-        const unsigned long long dt = gtime() - lb_t0;
-        atomicAdd(&g_lb_stats[0], dt);
-        atomicAdd(&g_lb_stats[1], 1ull);
-        atomicMax(&g_lb_stats[2], dt);
-#endif
       }
     }
     return;
@@ -390,12 +334,7 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   // pass 1 of local tile i: slice total and row carries.  false = no such tile.
   auto pass1 = [&](uint32_t i) -> bool {
     const uint32_t a = i % NA, q = i % NQ;
-    {
-      LB_T0();
-      if (!mbar_wait_or_stop(full_a0 + 8 * a, (i / NA) & 1u, abort_flag, nullptr, 0)) return false;
-      LB_ADD(4, threadIdx.x == 0);
-    }
-    LB_T0();
+    if (!mbar_wait_or_stop(full_a0 + 8 * a, (i / NA) & 1u, abort_flag, nullptr, 0)) return false;
     const unsigned long long tile = slot_tile[q];
     if (tile == kTileEnd) {
       if (lane == 0) *end_index = i;  // lets producer B, the look-back and the pass-2 warps leave
@@ -426,22 +365,16 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       mbar_arrive(p1done0 + 8 * q);
       mbar_arrive(empty_a0 + 8 * a);  // the stage can take the next first read
     }
-    LB_ADD(5, threadIdx.x == 0);
     return true;
   };
 
   // pass 2 of local tile k: the scan proper, seeded with everything before the slice
   auto pass2 = [&](uint32_t k) -> bool {
     const uint32_t b = k % NB, q = k % NQ;
-    {
-      LB_T0();
-      // producer B loads the tile only after its look-back; the second wait returns at once
-      // and makes tile_excl visible to this warp as well
-      if (!mbar_wait_or_stop(full_b0 + 8 * b, (k / NB) & 1u, abort_flag, end_index, k)) return false;
-      if (!mbar_wait_or_stop(resolved0 + 8 * q, (k / NQ) & 1u, abort_flag, end_index, k)) return false;
-      LB_ADD(3, threadIdx.x == kPass2Warp0 * 32);
-    }
-    LB_T0();
+    // producer B loads the tile only after its look-back; the second wait returns at once
+    // and makes tile_excl visible to this warp as well
+    if (!mbar_wait_or_stop(full_b0 + 8 * b, (k / NB) & 1u, abort_flag, end_index, k)) return false;
+    if (!mbar_wait_or_stop(resolved0 + 8 * q, (k / NQ) & 1u, abort_flag, end_index, k)) return false;
     const unsigned long long tile = slot_tile[q];
     const SliceView v = slice_view(ring_b + b * kTileBytes, tile);
     double carry = tile_excl[q];
@@ -482,8 +415,8 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       for (int j = 0; j < 8; ++j) {
         uint32_t ah[4], al[4];
         load_split(addr, j, ah, al);
-        scan_step_independent<SC, OUT32, TCU_LB_STREAM_STORES != 0>(j, ah, al, ops, rc, p.out, elem_base,
-                                                                    valid_elems, g, t, big);
+        scan_step_independent<SC, OUT32, /*kStream=*/true>(j, ah, al, ops, rc, p.out, elem_base,
+                                                           valid_elems, g, t, big);
       }
     }
     __syncwarp();
@@ -491,7 +424,6 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       mbar_arrive(empty_b0 + 8 * b);
       mbar_arrive(qfree0 + 8 * q);  // slot_tile, part, carries and tile_excl of the slot are free
     }
-    LB_ADD(6, threadIdx.x == kPass2Warp0 * 32);
     return true;
   };
 

@@ -27,19 +27,13 @@ namespace TCU_NS {
 constexpr int kUmmaRows       = 128;                               // rows (TMEM lanes) per tile
 constexpr int kUmmaTileElems  = kUmmaRows * kSwizzleRowElems;      // 8192 halves
 constexpr int kUmmaTileBytes  = kUmmaTileElems * 2;                // 16 KiB
-#ifndef TCU_UMMA_STAGES
-#define TCU_UMMA_STAGES 6
-#endif
 // Ring depth: 6 x 16 KiB in flight per SM measured fastest (1.03 of the copy
 // bandwidth at 2^28 elements); 8 stages give 0.98, 12 stages 0.90.
-constexpr int kUmmaStages     = TCU_UMMA_STAGES;
+constexpr int kUmmaStages     = 6;
 constexpr int kUmmaN          = 16;                                // accumulator columns per tile
 constexpr int kUmmaBBytes     = kUmmaN * kSwizzleRowElems * 2;     // 2 KiB
 constexpr int kUmmaThreads    = 6 * 32;
-#ifndef TCU_UMMA_ACC_STAGES
-#define TCU_UMMA_ACC_STAGES 4
-#endif
-constexpr int kUmmaAccStages  = TCU_UMMA_ACC_STAGES;               // accumulators in flight (power of two)
+constexpr int kUmmaAccStages  = 4;              // accumulators in flight (power of two)
 constexpr int kUmmaTmemCols   = kUmmaAccStages * kUmmaN < 32 ? 32 : kUmmaAccStages * kUmmaN;
 static_assert((kUmmaAccStages & (kUmmaAccStages - 1)) == 0 && kUmmaTmemCols <= 512 &&
               (kUmmaTmemCols & (kUmmaTmemCols - 1)) == 0, "TMEM columns: a power of two, 32..512");
@@ -115,10 +109,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     }
     s_failed = 0u;
     mbar_fence_init();
-#ifndef TCU_UMMA_EARLY_LOADS
-#define TCU_UMMA_EARLY_LOADS 1
-#endif
-    if constexpr (TCU_UMMA_EARLY_LOADS != 0) {
+    {
       // This thread is also the producer: it fills the ring right away, so the first tiles are
       // in flight while the others build B and allocate tensor memory.
       pdl_prologue();
@@ -158,7 +149,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       // the first kUmmaStages tiles were requested before the CTA-wide set-up (see above)
-      uint32_t i = TCU_UMMA_EARLY_LOADS != 0 ? kUmmaStages : 0;
+      uint32_t i = kUmmaStages;
       for (unsigned long long tile = blockIdx.x + (unsigned long long)i * gridDim.x; tile < num_tiles;
            tile += gridDim.x, ++i) {
         const uint32_t s = i % kUmmaStages, ph = (i / kUmmaStages) & 1u;

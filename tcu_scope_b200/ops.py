@@ -163,6 +163,11 @@ def full_scan(x: torch.Tensor, out_dtype=torch.float32, algo="auto",
     return out
 
 
+def num_sms() -> int:
+    """Streaming multiprocessors of the current device (the grid size of the persistent kernels)."""
+    return int(_lib.load().tcu_num_sms())
+
+
 def device_error(clear: bool = True) -> int:
     """Synchronise and return the device-side error bits (0 = none)."""
     bits = ctypes.c_uint(0)

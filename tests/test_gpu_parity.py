@@ -320,3 +320,24 @@ def test_host_buffers_match_device_path(tcu):
     ctx.run(tcu.OP_FULL_SCAN, h01, fs)
     assert oracle.np_check_f32(fs.numpy(), ref)[0] == 0
     ctx.close()
+
+
+def test_host_sweep_with_sizes_that_are_not_powers_of_two(tcu):
+    """Chunks of the sweep must hold whole segments of every size: with {48, 64} a chunk is a
+    multiple of 192, not of 64; small chunks make the array span many of them."""
+    ctx = tcu.HostContext(chunk_elements=1 << 14)  # the smallest staging buffer: one tile
+    sizes = [48, 64, 16]
+    n = 192 * 1000  # 12 chunks of 16320 elements (85 x 192) and a short one
+    h_in = torch.from_numpy(oracle.np_fill_f16(n, 45, 0).view(np.int16)).view(torch.float16).pin_memory()
+    outs = [torch.empty(n // s, dtype=torch.float32).pin_memory() for s in sizes]
+    ctx.reduce_sweep(h_in, sizes, outs)
+    for s, o in zip(sizes, outs):
+        assert oracle.np_check_f32(o.numpy(), oracle.np_segmented_reduce(bits(h_in), s))[0] == 0, s
+    # sizes whose common multiple exceeds the staging buffer are refused, not mangled
+    big = [16384, 48]
+    m = 16384 * 3 * 2
+    h2 = torch.zeros(m, dtype=torch.float16).pin_memory()
+    with pytest.raises(tcu.TcuError) as e:
+        ctx.reduce_sweep(h2, big, [torch.empty(m // s, dtype=torch.float32).pin_memory() for s in big])
+    assert e.value.status == 2
+    ctx.close()
