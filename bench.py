@@ -711,6 +711,27 @@ def cub_leg(torch, tcu, args):
     out["full_scan_f32"] = timed(oracle.CUB_FULL_SCAN, x, o, n30, n30, 5)
     out["note"] = ("cub::DeviceSegmentedReduce / DeviceScan::InclusiveSumByKey / DeviceReduce / "
                    "DeviceScan, fp16 inputs widened to fp32 by a transform iterator")
+    # Thrust, the reference's other comparison set (src/reduction/seg_thrust.cu:50,
+    # src/prefixsum/seg_thrust.cu:46, src/reduction/thrust.cu, src/prefixsum/thrust.cu)
+    th = {"seg_reduce_f32": {}, "seg_scan_f32": {}}
+
+    def thrust_timed(op, x, o, n, seg, reps):
+        def call():
+            rc = cub.tcu_thrust_run(op, x.data_ptr(), o.data_ptr(), n, seg, stream)
+            assert rc == 0, rc
+        ms, _ = time_op(torch, call, reps, 1)
+        return round(n / ms / 1e6, 1)
+    x = tcu.fill(torch.empty(n28, dtype=torch.float16, device="cuda"), 2024, 0)
+    for s in (16, 256, 16384):
+        o = torch.empty(n28 // s, dtype=torch.float32, device="cuda")
+        th["seg_reduce_f32"][str(s)] = thrust_timed(oracle.THRUST_REDUCE_BY_KEY, x, o, n28, s, 3)
+    o32 = torch.empty(n28, dtype=torch.float32, device="cuda")
+    for s in (16, 256, 4096):
+        th["seg_scan_f32"][str(s)] = thrust_timed(oracle.THRUST_SCAN_BY_KEY, x, o32, n28, s, 3)
+    th["full_scan_f32_2^28"] = thrust_timed(oracle.THRUST_SCAN, x, o32, n28, n28, 3)
+    th["full_reduce_2^28"] = thrust_timed(oracle.THRUST_REDUCE, x, o32, n28, n28, 3)
+    th["note"] = "thrust::reduce_by_key / inclusive_scan_by_key / inclusive_scan / reduce, 2^28 elements"
+    out["thrust"] = th
     return out
 
 

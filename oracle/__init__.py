@@ -248,8 +248,8 @@ _cub = None
 
 
 def cub_lib():
-    """oracle/libtcu_cub.so (``make -C oracle cub``): CUB device-wide reduce / scan on the same
-    inputs, the library baseline.  None when it has not been built."""
+    """oracle/libtcu_cub.so (``make -C oracle cub``): CUB device-wide and Thrust reduce / scan
+    on the same inputs, the library baselines.  None when it has not been built."""
     global _cub
     if _cub is not None:
         return _cub
@@ -259,11 +259,14 @@ def cub_lib():
     vp, sz, i32 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
     lib.tcu_cub_run.restype = i32
     lib.tcu_cub_run.argtypes = [i32, vp, vp, sz, sz, vp, ctypes.POINTER(sz), vp]
+    lib.tcu_thrust_run.restype = i32
+    lib.tcu_thrust_run.argtypes = [i32, vp, vp, sz, sz, vp]
     _cub = lib
     return lib
 
 
 CUB_FULL_REDUCE, CUB_SEG_REDUCE, CUB_FULL_SCAN, CUB_SEG_SCAN_F32, CUB_SEG_SCAN_F16 = range(5)
+THRUST_REDUCE, THRUST_REDUCE_BY_KEY, THRUST_SCAN, THRUST_SCAN_BY_KEY = range(4)
 
 
 def cub_temp_bytes(op: int, n: int, segment_size: int) -> int:

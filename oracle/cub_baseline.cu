@@ -2,13 +2,19 @@
 // CUDA toolkit) device-wide primitives, the comparison set of the reference
 // (cub::DeviceReduce::Sum, src/reduction/cub.cu:46; DeviceSegmentedReduce::Sum,
 // src/reduction/seg_cub_device.cu:61; DeviceScan::InclusiveSum,
-// src/prefixsum/cub.cu:44; scans by key stand in for thrust::inclusive_scan_by_key,
+// src/prefixsum/cub.cu:44) and Thrust (thrust::reduce, src/reduction/thrust.cu;
+// thrust::reduce_by_key, src/reduction/seg_thrust.cu:50; thrust::inclusive_scan,
+// src/prefixsum/thrust.cu; thrust::inclusive_scan_by_key,
 // src/prefixsum/seg_thrust.cu:46).  TEST / BASELINE INFRASTRUCTURE ONLY: never
 // linked into the library.  Inputs are fp16 and are widened to fp32 on the fly,
 // so the library calls accumulate in fp32 like the kernels they are compared with.
 #include <cub/cub.cuh>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <thrust/execution_policy.h>
+#include <thrust/iterator/discard_iterator.h>
+#include <thrust/reduce.h>
+#include <thrust/scan.h>
 
 namespace {
 
@@ -67,4 +73,39 @@ extern "C" int tcu_cub_run(int op, const void* d_in, void* d_out, size_t n, size
     default: break;
   }
   return e == cudaSuccess ? 0 : (int)e;
+}
+
+// The Thrust forms of the same operations (Thrust allocates its own temporary storage per
+// call, as it does in the reference's drivers).  op: 0 thrust::reduce -> float[1] (the value
+// comes back through the host, as the reference uses it); 1 thrust::reduce_by_key ->
+// float[segs]; 2 thrust::inclusive_scan -> float[n]; 3 thrust::inclusive_scan_by_key -> float[n].
+extern "C" int tcu_thrust_run(int op, const void* d_in, void* d_out, size_t n, size_t segment_size,
+                              void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  InIt in(static_cast<const __half*>(d_in), HalfToFloat());
+  auto pol = thrust::cuda::par.on(st);
+  KeyIt keys(cub::CountingInputIterator<long long>(0), SegmentOf{(long long)segment_size});
+  try {
+    switch (op) {
+      case 0: {
+        const float total = thrust::reduce(pol, in, in + n, 0.0f);
+        return cudaMemcpyAsync(d_out, &total, sizeof(total), cudaMemcpyHostToDevice, st) == cudaSuccess &&
+                       cudaStreamSynchronize(st) == cudaSuccess
+                   ? 0
+                   : 1;
+      }
+      case 1:
+        thrust::reduce_by_key(pol, keys, keys + n, in, thrust::make_discard_iterator(),
+                              static_cast<float*>(d_out));
+        return 0;
+      case 2: thrust::inclusive_scan(pol, in, in + n, static_cast<float*>(d_out)); return 0;
+      case 3:
+        thrust::inclusive_scan_by_key(pol, keys, keys + n, in, static_cast<float*>(d_out));
+        return 0;
+      default: return (int)cudaErrorInvalidValue;
+    }
+  } catch (...) {
+    cudaGetLastError();
+    return 2;
+  }
 }

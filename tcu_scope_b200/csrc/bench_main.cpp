@@ -11,10 +11,17 @@
 // the reference's tooling reads its output unchanged.  Google Benchmark itself
 // is not needed.
 //
-// The WARPS_PER_BLOCK / SEGMENT_SIZE template arguments of the reference's
-// names select launch shapes of its kernels; here every such name runs the one
-// persistent kernel of the family (8 consumer warps per CTA), so the argument
-// is kept in the name for compatibility and reported as "warps_per_block".
+// The WARPS_PER_BLOCK / SEGMENTS_PER_WARP / SEGMENT_SIZE template arguments of
+// the reference's names select launch shapes of its kernels.  This library picks
+// its launch shape itself, per segment class (persistent CTAs of 8 or 16
+// consumer warps, one or two per SM), so those arguments are INERT here: they
+// are kept in the name so that result files keep their names, reported as
+// "warps_per_block" like the reference does, and every result carries a
+// "label" saying so.  The same goes for the CUDA_UNSAFE_WMMA_* names
+// (src/unsafe_reduction, src/unsafe_prefixsum): their one difference in the
+// reference -- the constant matrix is written straight into fragment registers
+// instead of being staged through shared memory -- is how every kernel of this
+// library builds its constant operand.
 //
 //   tcu_bench --benchmark_filter='SEGMENTED_REDUCTION_16N<8>.*segment_size:16/' \
 //             --benchmark_out=results.json --benchmark_out_format=json
@@ -49,6 +56,7 @@ struct Options {
   int algo          = TCU_ALGO_AUTO;
   int out_type      = -1;     // -1: fp32 for reductions and the full scan, fp16 for segmented scans
   int min_log2 = 12, max_log2 = 30;  // src/reduction/args.hpp:39-40
+  int num_gpus = 1;  // > 1: the array is cut into one contiguous shard per device (whole segments)
 };
 
 struct Benchmark {
@@ -64,6 +72,7 @@ struct Result {
   bool error = false;
   std::string error_message;
   long long iterations = 0;
+  std::string label;
   double real_time_ns = 0, cpu_time_ns = 0;
   std::vector<std::pair<std::string, double>> counters;
 };
@@ -146,8 +155,19 @@ void add_full(std::vector<Benchmark>& out, const Options& o, const std::string& 
       }
 }
 
+void add_family(std::vector<Benchmark>& b, const Options& o, const std::string& prefix);
+
 std::vector<Benchmark> registry(const Options& o) {
   std::vector<Benchmark> b;
+  add_family(b, o, "CUDA_WMMA_");
+  // src/unsafe_reduction/seg_wmma_16n.cu:183-229, src/unsafe_prefixsum/seg_wmma_16n.cu:188-194
+  // and their siblings: the same registrations under the CUDA_UNSAFE_WMMA_ prefix
+  add_family(b, o, "CUDA_UNSAFE_WMMA_");
+  return b;
+}
+
+void add_family(std::vector<Benchmark>& b, const Options& o, const std::string& prefix) {
+  const bool unsafe = prefix.find("UNSAFE") != std::string::npos;
   const std::initializer_list<size_t> k16n  = {16, 32, 64, 128, 256, 512, 1024};
   const std::initializer_list<size_t> k256n = {256, 512, 1024, 2048, 4096, 8192, 16384};
   // Every variant name of the reference maps onto the one kernel family of this
@@ -156,45 +176,47 @@ std::vector<Benchmark> registry(const Options& o) {
   // src/reduction/seg_wmma_16n.cu:215-221, seg_wmma_16n_opt.cu:209-221, seg_wmma_16n_block.cu:213-235,
   // seg_wmma_256n.cu:223-229, seg_wmma_256n_block.cu, seg_wmma_16.cu:132-147, seg_wmma_256.cu
   for (const char* v : {"", "_OPT", "_BLOCK"}) {
-    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_REDUCTION_16N") + v, TCU_OP_SEGMENTED_REDUCE, k16n);
-    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_16N") + v, TCU_OP_SEGMENTED_REDUCE, 16, 30);
+    add_segmented(b, o, (prefix + "SEGMENTED_REDUCTION_16N") + v, TCU_OP_SEGMENTED_REDUCE, k16n);
+    add_tune(b, (prefix + "TUNE_SEGMENTED_REDUCTION_16N") + v, TCU_OP_SEGMENTED_REDUCE, 16, 30);
   }
   for (const char* v : {"", "_BLOCK"}) {
-    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, k256n);
-    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, 256, 22);
-    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, 256, 30);
+    add_segmented(b, o, (prefix + "SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, k256n);
+    add_tune(b, (prefix + "TUNE_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, 256, 22);
+    add_tune(b, (prefix + "TUNE_SEGMENTED_REDUCTION_256N") + v, TCU_OP_SEGMENTED_REDUCE, 256, 30);
   }
-  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_REDUCTION_16", TCU_OP_SEGMENTED_REDUCE, 16);
-  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_REDUCTION_256", TCU_OP_SEGMENTED_REDUCE, 256);
+  add_fixed(b, o, prefix + "SEGMENTED_REDUCTION_16", TCU_OP_SEGMENTED_REDUCE, 16);
+  add_fixed(b, o, prefix + "SEGMENTED_REDUCTION_256", TCU_OP_SEGMENTED_REDUCE, 256);
   // src/reduction/wmma_2kers.cu:172-194, wmma_2kers_block.cu:173-198, wmma_cg.cu:171-195,
   // wmma_atomic.cu:163-185
-  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BASE_16", TCU_OP_FULL_REDUCE, 16);
-  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BASE_256", TCU_OP_FULL_REDUCE, 16);
-  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BLOCK_BASE_16", TCU_OP_FULL_REDUCE, 256);
-  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_2KERS_BLOCK_BASE_256", TCU_OP_FULL_REDUCE, 256);
-  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_CG", TCU_OP_FULL_REDUCE, 1024);
-  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_ATOMIC_W_ATOMIC_BALLOT", TCU_OP_FULL_REDUCE, 16);
-  add_full(b, o, "CUDA_WMMA_FULL_REDUCTION_ATOMIC_W_BLOCK_SYNC", TCU_OP_FULL_REDUCE, 16);
+  add_full(b, o, prefix + "FULL_REDUCTION_2KERS_BASE_16", TCU_OP_FULL_REDUCE, 16);
+  add_full(b, o, prefix + "FULL_REDUCTION_2KERS_BASE_256", TCU_OP_FULL_REDUCE, 16);
+  add_full(b, o, prefix + "FULL_REDUCTION_2KERS_BLOCK_BASE_16", TCU_OP_FULL_REDUCE, 256);
+  add_full(b, o, prefix + "FULL_REDUCTION_2KERS_BLOCK_BASE_256", TCU_OP_FULL_REDUCE, 256);
+  add_full(b, o, prefix + "FULL_REDUCTION_CG", TCU_OP_FULL_REDUCE, 1024);
+  // the unsafe tree registers these two without the underscore after WMMA
+  // (src/unsafe_reduction/wmma_atomic.cu:166,172); the name is kept as it is there
+  const std::string atomic_prefix = unsafe ? "CUDA_UNSAFE_WMMA" : prefix;
+  add_full(b, o, atomic_prefix + "FULL_REDUCTION_ATOMIC_W_ATOMIC_BALLOT", TCU_OP_FULL_REDUCE, 16);
+  add_full(b, o, atomic_prefix + "FULL_REDUCTION_ATOMIC_W_BLOCK_SYNC", TCU_OP_FULL_REDUCE, 16);
   // src/prefixsum/seg_wmma_16n.cu:217-223, seg_wmma_16n_opt.cu:211-223, seg_wmma_16n_block.cu:216-238,
   // seg_wmma_256n.cu:216-222, seg_wmma_256n_block.cu:211-233, seg_wmma_16.cu, seg_wmma_256.cu
   for (const char* v : {"", "_OPT", "_BLOCK"}) {
-    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_PREFIXSUM_16N") + v, TCU_OP_SEGMENTED_SCAN, k16n);
-    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_PREFIXSUM_16N") + v, TCU_OP_SEGMENTED_SCAN, 16, 30);
+    add_segmented(b, o, (prefix + "SEGMENTED_PREFIXSUM_16N") + v, TCU_OP_SEGMENTED_SCAN, k16n);
+    add_tune(b, (prefix + "TUNE_SEGMENTED_PREFIXSUM_16N") + v, TCU_OP_SEGMENTED_SCAN, 16, 30);
   }
   for (const char* v : {"", "_BLOCK"}) {
-    add_segmented(b, o, std::string("CUDA_WMMA_SEGMENTED_PREFIXSUM_256N") + v, TCU_OP_SEGMENTED_SCAN, k256n);
-    add_tune(b, std::string("CUDA_WMMA_TUNE_SEGMENTED_PREFIXSUM_256N") + v, TCU_OP_SEGMENTED_SCAN, 256, 30);
+    add_segmented(b, o, (prefix + "SEGMENTED_PREFIXSUM_256N") + v, TCU_OP_SEGMENTED_SCAN, k256n);
+    add_tune(b, (prefix + "TUNE_SEGMENTED_PREFIXSUM_256N") + v, TCU_OP_SEGMENTED_SCAN, 256, 30);
   }
-  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_PREFIXSUM_16", TCU_OP_SEGMENTED_SCAN, 16);
-  add_fixed(b, o, "CUDA_WMMA_SEGMENTED_PREFIXSUM_256", TCU_OP_SEGMENTED_SCAN, 256);
+  add_fixed(b, o, prefix + "SEGMENTED_PREFIXSUM_16", TCU_OP_SEGMENTED_SCAN, 16);
+  add_fixed(b, o, prefix + "SEGMENTED_PREFIXSUM_256", TCU_OP_SEGMENTED_SCAN, 256);
   // src/prefixsum/wmma_3kers.cu:161-183, wmma_3kers_block.cu:175-185, wmma_cg.cu:183-207,
   // wmma_atomic.cu:176-200
-  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_3KERS", TCU_OP_FULL_SCAN, 16);
-  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_3KERS_BLOCK", TCU_OP_FULL_SCAN, 256);
-  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_CG", TCU_OP_FULL_SCAN, 1024);
-  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_ATOMIC_W_ATOMIC_BALLOT", TCU_OP_FULL_SCAN, 1024);
-  add_full(b, o, "CUDA_WMMA_FULL_PREFIXSUM_ATOMIC_W_BLOCK_SYNC", TCU_OP_FULL_SCAN, 1024);
-  return b;
+  add_full(b, o, prefix + "FULL_PREFIXSUM_3KERS", TCU_OP_FULL_SCAN, 16);
+  add_full(b, o, prefix + "FULL_PREFIXSUM_3KERS_BLOCK", TCU_OP_FULL_SCAN, 256);
+  add_full(b, o, prefix + "FULL_PREFIXSUM_CG", TCU_OP_FULL_SCAN, 1024);
+  add_full(b, o, prefix + "FULL_PREFIXSUM_ATOMIC_W_ATOMIC_BALLOT", TCU_OP_FULL_SCAN, 1024);
+  add_full(b, o, prefix + "FULL_PREFIXSUM_ATOMIC_W_BLOCK_SYNC", TCU_OP_FULL_SCAN, 1024);
 }
 
 // ------------------------------------------------------------- validation
@@ -336,6 +358,7 @@ Result run_one(const Benchmark& b, const Options& o) {
       if (!msg.empty()) throw msg;
     }
     r.iterations   = iters;
+    r.label        = "template arguments are inert: the library picks its launch shape per segment class";
     r.real_time_ns = total_ms * 1e6 / iters;
     r.cpu_time_ns  = host_ms * 1e6 / iters;
     const double secs = total_ms * 1e-3;
@@ -354,6 +377,187 @@ Result run_one(const Benchmark& b, const Options& o) {
       if (!have) r.counters.push_back({kv.first, (double)kv.second});
     }
   } catch (const std::string& e) {  // the reference's SkipWithError (seg_wmma_16n.cu:126-134)
+    r.error = true;
+    r.error_message = e;
+    cudaGetLastError();
+  }
+  cleanup();
+  return r;
+}
+
+// --num_gpus=G: one array, G contiguous shards of whole segments, one per device, driven by
+// this one host thread (the reference is single-device, src/init/cuda.cpp:45).  Segmented
+// operations need no communication; the full reduction and the full scan go through
+// tcu_mgpu_* (the shard totals are stored by the kernels into every device's memory).  The
+// time of an iteration is the longest of the devices' own event intervals; "flops" counts
+// the elements of all shards.
+Result run_one_multi(const Benchmark& b, const Options& o) {
+  Result r;
+  r.name = b.name;
+  const int G = o.num_gpus;
+  const bool reduce = b.op == TCU_OP_SEGMENTED_REDUCE || b.op == TCU_OP_FULL_REDUCE;
+  const bool full   = b.op == TCU_OP_FULL_REDUCE || b.op == TCU_OP_FULL_SCAN;
+  const int out_type = b.op == TCU_OP_FULL_REDUCE ? TCU_OUT_F32
+                       : (o.out_type >= 0 ? o.out_type
+                                          : (reduce || b.op == TCU_OP_FULL_SCAN ? TCU_OUT_F32 : TCU_OUT_F16));
+  const size_t osz = out_type == TCU_OUT_F32 ? 4 : 2;
+  struct Dev {
+    void *in = nullptr, *out = nullptr, *ws = nullptr;
+    cudaStream_t st = nullptr;
+    cudaEvent_t start = nullptr, stop = nullptr;
+    tcu_mgpu_ctx* ctx = nullptr;
+    size_t first = 0, elems = 0, units = 0;  // shard: first element, elements, segments
+    size_t ws_bytes = 0;
+  };
+  std::vector<Dev> dev(G);
+  auto cleanup = [&]() {
+    for (int d = 0; d < G; ++d) {
+      cudaSetDevice(d);
+      cudaDeviceSynchronize();
+    }
+    for (int d = 0; d < G; ++d) {  // every device is idle: nobody stores into a peer any more
+      cudaSetDevice(d);
+      Dev& v = dev[d];
+      if (v.ctx) tcu_mgpu_ctx_destroy(v.ctx);
+      if (v.in) cudaFree(v.in);
+      if (v.out) cudaFree(v.out);
+      if (v.ws) cudaFree(v.ws);
+      if (v.start) cudaEventDestroy(v.start);
+      if (v.stop) cudaEventDestroy(v.stop);
+      if (v.st) cudaStreamDestroy(v.st);
+    }
+    cudaSetDevice(o.device);
+  };
+  try {
+    // units of sharding: whole segments, or groups of 16 elements for the full operations
+    const size_t unit = full ? 16 : b.segment_size;
+    const size_t units = b.num_elements / unit;
+    const int dist = o.const_fill ? TCU_DIST_CONST_0P001 : (full ? TCU_DIST_UNIFORM_01 : TCU_DIST_UNIFORM_PM1);
+    std::vector<tcu_mgpu_ctx*> group(G, nullptr);
+    for (int d = 0; d < G; ++d) {
+      CHECK_CUDA(cudaSetDevice(d));
+      Dev& v = dev[d];
+      const size_t ub = units * d / G, ue = units * (d + 1) / G;
+      v.first = ub * unit;
+      v.elems = (ue - ub) * unit;
+      v.units = ue - ub;
+      CHECK_CUDA(cudaStreamCreateWithFlags(&v.st, cudaStreamNonBlocking));
+      CHECK_CUDA(cudaEventCreate(&v.start));
+      CHECK_CUDA(cudaEventCreate(&v.stop));
+      CHECK_CUDA(cudaMalloc(&v.in, std::max<size_t>(v.elems * 2, 16)));
+      CHECK_CUDA(cudaMalloc(&v.out, std::max<size_t>((reduce ? (full ? 1 : v.units) : v.elems) * osz, 16)));
+      v.ws_bytes = full ? 0 : tcu_workspace_bytes(b.op, v.elems, b.segment_size);
+      if (v.ws_bytes) CHECK_CUDA(cudaMalloc(&v.ws, v.ws_bytes));
+      check_tcu(tcu_fill_f16(v.in, v.elems, o.seed, v.first, dist, v.st), "tcu_fill_f16");
+      if (full) {
+        check_tcu(tcu_mgpu_ctx_create(&v.ctx, d, G, nullptr), "tcu_mgpu_ctx_create");
+        group[d] = v.ctx;
+      }
+    }
+    if (full)
+      for (int d = 0; d < G; ++d) check_tcu(tcu_mgpu_ctx_connect_local(dev[d].ctx, group.data()), "tcu_mgpu_ctx_connect_local");
+    auto call = [&](int d) {
+      Dev& v = dev[d];
+      switch (b.op) {
+        case TCU_OP_SEGMENTED_REDUCE:
+          return tcu_segmented_reduce_f16(v.in, v.out, out_type, v.units, b.segment_size, o.algo, v.ws, v.ws_bytes, v.st);
+        case TCU_OP_SEGMENTED_SCAN:
+          return tcu_segmented_scan_f16(v.in, v.out, out_type, v.units, b.segment_size, o.algo, v.ws, v.ws_bytes, v.st);
+        case TCU_OP_FULL_REDUCE: return tcu_mgpu_full_reduce_f16(v.ctx, v.in, (float*)v.out, nullptr, v.elems, v.st);
+        default: return tcu_mgpu_full_scan_f16(v.ctx, v.in, v.out, out_type, v.elems, v.st);
+      }
+    };
+    auto round = [&](bool timed) {
+      for (int d = 0; d < G; ++d) {
+        CHECK_CUDA(cudaSetDevice(d));
+        if (timed) CHECK_CUDA(cudaEventRecord(dev[d].start, dev[d].st));
+        check_tcu(call(d), "call");
+        if (timed) CHECK_CUDA(cudaEventRecord(dev[d].stop, dev[d].st));
+      }
+      float worst = 0.f;
+      for (int d = 0; d < G; ++d) {
+        CHECK_CUDA(cudaSetDevice(d));
+        CHECK_CUDA(cudaStreamSynchronize(dev[d].st));
+        if (timed) {
+          float ms = 0.f;
+          CHECK_CUDA(cudaEventElapsedTime(&ms, dev[d].start, dev[d].stop));
+          worst = std::max(worst, ms);
+        }
+      }
+      return worst;
+    };
+    for (int w = 0; w < 3; ++w) round(false);
+    double total_ms = 0.0;
+    long long iters = 0;
+    const auto host_t0 = std::chrono::steady_clock::now();
+    while ((total_ms < o.min_time * 1e3 && iters < 100000) || iters < 3) {
+      total_ms += round(true);
+      ++iters;
+    }
+    const double host_ms =
+        std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
+    for (int d = 0; d < G; ++d) {
+      CHECK_CUDA(cudaSetDevice(d));
+      unsigned int bits = 0;
+      check_tcu(tcu_device_error(&bits, 1), "device error word");
+    }
+    if (o.validate) {
+      // every shard against the sequential sum of ITS segments; the full scan against the
+      // running sum continued from the earlier shards (their totals summed on the host)
+      double carry = 0.0;
+      for (int d = 0; d < G; ++d) {
+        CHECK_CUDA(cudaSetDevice(d));
+        const Dev& v = dev[d];
+        if (!full) {
+          Benchmark sb = b;
+          sb.num_segments = v.units;
+          sb.num_elements = v.elems;
+          const std::string msg = validate(sb, out_type == TCU_OUT_F32, v.in, v.out);
+          if (!msg.empty()) throw "device " + std::to_string(d) + ": " + msg;
+          continue;
+        }
+        std::vector<uint16_t> in(v.elems);
+        CHECK_CUDA(cudaMemcpy(in.data(), v.in, v.elems * 2, cudaMemcpyDeviceToHost));
+        std::vector<uint8_t> out(b.op == TCU_OP_FULL_SCAN ? v.elems * osz : 0);
+        if (!out.empty()) CHECK_CUDA(cudaMemcpy(out.data(), v.out, out.size(), cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < v.elems; ++i) {
+          carry += half_to_double(in[i]);
+          if (b.op != TCU_OP_FULL_SCAN) continue;
+          const double got = out_type == TCU_OUT_F32 ? (double)((const float*)out.data())[i]
+                                                     : half_to_double(((const uint16_t*)out.data())[i]);
+          if (!close_enough(got, carry, out_type == TCU_OUT_F32))
+            throw "validation failed: device " + std::to_string(d) + " element " + std::to_string(i);
+        }
+      }
+      if (b.op == TCU_OP_FULL_REDUCE)
+        for (int d = 0; d < G; ++d) {  // every device holds the sum over all shards
+          CHECK_CUDA(cudaSetDevice(d));
+          float got = 0.f;
+          CHECK_CUDA(cudaMemcpy(&got, dev[d].out, 4, cudaMemcpyDeviceToHost));
+          if (!close_enough(got, carry, true)) throw "validation failed: total on device " + std::to_string(d);
+        }
+    }
+    r.iterations   = iters;
+    r.label        = "template arguments are inert: the library picks its launch shape per segment class";
+    r.real_time_ns = total_ms * 1e6 / iters;
+    r.cpu_time_ns  = host_ms * 1e6 / iters;
+    const double secs = total_ms * 1e-3;
+    const double n = (double)b.num_elements;
+    const double bytes_alg = n * 2 + (reduce ? (double)b.num_segments : n) * osz;
+    r.counters = {{"num_segments", (double)b.num_segments},
+                  {"segment_size", (double)b.segment_size},
+                  {"num_elements", n},
+                  {"warps_per_block", (double)b.warps_per_block},
+                  {"flops", (double)iters * n / secs},
+                  {"bytes_algorithmic", bytes_alg},
+                  {"gbytes_per_s", (double)iters * bytes_alg / secs / 1e9},
+                  {"num_gpus", (double)G}};
+    for (auto& kv : b.extra_counters) {
+      bool have = false;
+      for (auto& c : r.counters) if (c.first == kv.first) { c.second = (double)kv.second; have = true; }
+      if (!have) r.counters.push_back({kv.first, (double)kv.second});
+    }
+  } catch (const std::string& e) {
     r.error = true;
     r.error_message = e;
     cudaGetLastError();
@@ -389,6 +593,7 @@ void write_json(const std::string& path, const std::vector<Result>& results, con
     std::fprintf(f, "      \"iterations\": %lld,\n      \"real_time\": %.6e,\n      \"cpu_time\": %.6e,\n"
                     "      \"time_unit\": \"ns\"",
                  r.iterations, r.real_time_ns, r.cpu_time_ns);
+    if (!r.label.empty()) std::fprintf(f, ",\n      \"label\": \"%s\"", json_escape(r.label).c_str());
     for (auto& c : r.counters) std::fprintf(f, ",\n      \"%s\": %.6e", c.first.c_str(), c.second);
     std::fprintf(f, "\n    }%s\n", i + 1 < results.size() ? "," : "");
   }
@@ -425,6 +630,7 @@ int main(int argc, char** argv) {
     else if (flag_value(argv[i], "--out_type", &v)) o.out_type = v == "f32" ? TCU_OUT_F32 : TCU_OUT_F16;
     else if (flag_value(argv[i], "--min_log2", &v)) o.min_log2 = std::atoi(v.c_str());
     else if (flag_value(argv[i], "--max_log2", &v)) o.max_log2 = std::atoi(v.c_str());
+    else if (flag_value(argv[i], "--num_gpus", &v)) o.num_gpus = std::atoi(v.c_str());
     else {
       std::printf("usage: tcu_bench [--benchmark_filter=REGEX] [--benchmark_list_tests] "
                   "[--benchmark_out=FILE] [--benchmark_min_time=S]\n"
@@ -454,11 +660,16 @@ int main(int argc, char** argv) {
     return 1;
   }
   if (o.device >= count) o.device = 0;  // as src/init/cuda.cpp:41-43
+  if (o.num_gpus < 1 || o.num_gpus > count || o.num_gpus > TCU_MGPU_MAX_RANKS) {
+    std::fprintf(stderr, "--num_gpus=%d: this machine has %d device(s)\n", o.num_gpus, count);
+    return 1;
+  }
+  if (o.num_gpus > 1) o.device = 0;  // shards go to devices 0 .. G-1
   cudaSetDevice(o.device);
   std::printf("%-100s %14s %12s %16s\n", "Benchmark", "Time(ns)", "Iterations", "Gelem/s");
   std::vector<Result> results;
   for (auto& b : selected) {
-    Result r = run_one(b, o);
+    Result r = o.num_gpus > 1 ? run_one_multi(b, o) : run_one(b, o);
     if (r.error) {
       std::printf("%-100s ERROR OCCURRED: '%s'\n", r.name.c_str(), r.error_message.c_str());
     } else {

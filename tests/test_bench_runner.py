@@ -47,10 +47,25 @@ def test_registered_names_match_the_reference_format(bench_binary):
         assert list_names(bench_binary, "^" + fam + "<"), fam
 
 
+def test_unsafe_names_are_registered_like_the_safe_ones(bench_binary):
+    # src/unsafe_reduction/seg_wmma_16n.cu:183-229, src/unsafe_prefixsum/seg_wmma_16n.cu:188-194 and
+    # siblings register the same sweeps under CUDA_UNSAFE_WMMA_*
+    safe = list_names(bench_binary, r"^CUDA_WMMA_")
+    unsafe = list_names(bench_binary, r"^CUDA_UNSAFE_WMMA")
+    assert len(safe) == len(unsafe) > 10000
+    renamed = {n.replace("CUDA_WMMA_", "CUDA_UNSAFE_WMMA_", 1) for n in safe}
+    # the unsafe tree spells two families without the underscore (src/unsafe_reduction/wmma_atomic.cu:166,172)
+    renamed = {n.replace("CUDA_UNSAFE_WMMA_FULL_REDUCTION_ATOMIC", "CUDA_UNSAFE_WMMAFULL_REDUCTION_ATOMIC")
+               for n in renamed}
+    assert renamed == set(unsafe)
+    assert ("CUDA_UNSAFE_WMMA_TUNE_SEGMENTED_REDUCTION_16N<16>/num_segments:67108864/segment_size:16/"
+            "base_segment_size:16/max_elements_log2:30/manual_time") in unsafe
+
+
 @pytest.mark.gpu
 def test_runner_output_has_the_reference_schema(bench_binary, tmp_path):
     out = tmp_path / "r.json"
-    flt = (r"(SEGMENTED_REDUCTION_16N<8>.*segment_size:16/num_elements:(4096|16777216)/|"
+    flt = (r"^CUDA_WMMA_(SEGMENTED_REDUCTION_16N<8>.*segment_size:16/num_elements:(4096|16777216)/|"
            r"SEGMENTED_PREFIXSUM_256N<8>.*segment_size:4096/num_elements:1048576/|"
            r"FULL_REDUCTION_2KERS_BASE_256<256, 8>/num_elements:1048576/|"
            r"FULL_PREFIXSUM_3KERS<256, 8>/num_elements:4194304/|"
@@ -69,3 +84,25 @@ def test_runner_output_has_the_reference_schema(bench_binary, tmp_path):
         assert b["flops"] > 0 and b["time_unit"] == "ns"
         # "flops" is elements per second: consistent with the manual time
         assert b["flops"] == pytest.approx(b["num_elements"] / (b["real_time"] * 1e-9), rel=1e-3)
+        assert "inert" in b["label"]  # what the template arguments in the name mean here
+
+
+@pytest.mark.gpu
+def test_runner_on_several_gpus(bench_binary, tmp_path):
+    import torch
+    gpus = torch.cuda.device_count()
+    if gpus < 2:
+        pytest.skip("needs two or more GPUs")
+    out = tmp_path / "m.json"
+    flt = (r"^CUDA_(UNSAFE_)?WMMA_(SEGMENTED_REDUCTION_256N<8>.*segment_size:1024/num_elements:4194304/|"
+           r"SEGMENTED_PREFIXSUM_16N<8>.*segment_size:64/num_elements:4194304/|"
+           r"FULL_REDUCTION_2KERS_BASE_256<256, 8>/num_elements:16777216/|"
+           r"FULL_PREFIXSUM_3KERS<256, 8>/num_elements:16777216/)")
+    g = min(gpus, 4)
+    subprocess.run([BENCH, f"--benchmark_filter={flt}", f"--benchmark_out={out}", f"--num_gpus={g}",
+                    "--benchmark_min_time=0.02", "--validate"], check=True, capture_output=True, text=True)
+    j = json.loads(out.read_text())
+    assert len(j["benchmarks"]) == 8
+    for b in j["benchmarks"]:
+        assert not b.get("error_occurred", False), b
+        assert b["num_gpus"] == g and b["flops"] > 0

@@ -63,3 +63,60 @@ def test_static_scratch_scan_rejects_oversize_input():
     assert b"scratch" in lib.tcu_status_string(st)
     torch.cuda.synchronize()
     assert torch.all(out == 0)
+
+
+def test_static_scratch_scan_allocates_nothing_and_takes_a_seed():
+    """Free device memory is the same before and after the calls (the scratch is part of the
+    library's device image, not an allocation), and the multi-GPU seed -- the totals of the
+    earlier shards -- goes through this entry point as it does through tcu_full_scan_f16."""
+    import tcu_scope_b200 as tcu
+    lib = tcu._lib.load()
+    n = (1 << 21) + 16 * 5
+    x = torch.empty(n, dtype=torch.float16, device="cuda")
+    tcu.fill(x, 8, 0, "uniform_01")
+    got = torch.empty(n, dtype=torch.float32, device="cuda")
+    totals = torch.tensor([1000.5, 250.25, 7.0], dtype=torch.float64, device="cuda")
+    want = tcu.full_scan(x, out_dtype=torch.float32, shard_totals=totals, shard_index=2)
+    # first call on this device (if no other test made it) does the one-time address look-up
+    assert lib.tcu_full_scan_f16_static(x.data_ptr(), got.data_ptr(), OUT_F32, n, totals.data_ptr(), 2,
+                                        0, _stream()) == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert lib.tcu_full_scan_f16_static(x.data_ptr(), got.data_ptr(), OUT_F32, n,
+                                            totals.data_ptr(), 2, 0, _stream()) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "the call changed the amount of free device memory"
+    assert torch.equal(got, want)
+    xb = x.cpu().view(torch.int16).numpy().view(np.uint16)
+    ref = oracle.c_segmented_scan(xb, n) + 1250.75  # the two earlier shards
+    assert oracle.np_check_f32(got.cpu().numpy(), ref, 1e-3, 1e-5)[0] == 0
+    assert tcu.device_error() == 0
+
+
+def test_static_scratch_scan_at_its_size_limit():
+    """2^30 elements is the largest input the built-in scratch is sized for: accepted, and equal
+    to the scan with a caller-made workspace."""
+    import tcu_scope_b200 as tcu
+    lib = tcu._lib.load()
+    n = 1 << 30
+    free, _ = torch.cuda.mem_get_info()
+    if free < 12 * (1 << 30):
+        pytest.skip("needs 12 GiB of free device memory")
+    x = torch.empty(n, dtype=torch.float16, device="cuda")
+    tcu.fill(x, 9, 0, "uniform_01")
+    got = torch.empty(n, dtype=torch.float32, device="cuda")
+    assert lib.tcu_full_scan_f16_static(x.data_ptr(), got.data_ptr(), OUT_F32, n, None, 0, 0,
+                                        _stream()) == 0
+    want = tcu.full_scan(x, out_dtype=torch.float32)
+    # The look-back adds tile aggregates in the order they become available; at 2^29 and beyond a
+    # prefix no longer fits a double exactly, so two runs may round a handful of the 2^30 outputs
+    # to neighbouring floats: compare to one float32 ulp (the tests' tolerance is 1e-3 relative).
+    want.sub_(got).abs_()
+    want.div_(got.abs().clamp_(min=1.0))
+    assert float(want.max()) <= 1.2e-7
+    del want
+    tail = got[-(1 << 16):].cpu().numpy()
+    assert np.all(np.diff(tail) >= 0) and abs(tail[-1] / (n / 2) - 1) < 1e-3  # mean of [0,1) inputs
+    assert tcu.device_error() == 0
