@@ -70,7 +70,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--algo", default="auto", choices=["auto", "mma", "shuffle", "tcgen05"],
-                    help="tcgen05 only exists for segment sizes up to 2048: use it with --profile reduce")
+                    help="tcgen05 covers reductions up to 2048 and scans up to 16384 elements per "
+                         "segment: use it with --profile reduce or --profile scan")
     ap.add_argument("--log2-elems", type=int, default=LOG2_ELEMS,
                     help="elements per GPU (default 28, the reference sweep's size)")
     ap.add_argument("--profile", default=None, choices=["reduce", "scan", "full"],
@@ -79,9 +80,9 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other configurations, the e2e leg and the CPU baseline")
     args = ap.parse_args()
-    if args.algo == "tcgen05" and args.profile != "reduce":
-        ap.error("--algo tcgen05 covers segment sizes up to 2048 only: use it with --profile reduce "
-                 "(the timed sweep reports it under ablation_tensor_core_vs_shuffle)")
+    if args.algo == "tcgen05" and args.profile not in ("reduce", "scan"):
+        ap.error("--algo tcgen05 does not cover every size of the sweep: use it with --profile reduce "
+                 "or --profile scan (the timed run reports it under ablation_tensor_core_vs_shuffle)")
     return args
 
 
@@ -777,10 +778,22 @@ def ablation_leg(torch, tcu, args):
         ms, _ = time_op(torch, call, 10, 3)
         red[str(s)] = round(n / ms / 1e6, 1)
     out["reduce"]["tcgen05"] = red
+    sc = {}
+    for s, dt in [(16, torch.float16), (256, torch.float16), (2048, torch.float16), (4096, torch.float32)]:
+        o = torch.empty(n, dtype=dt, device="cuda")
+        for algo in ("mma", "tcgen05"):
+            def call():
+                k[0] += 1
+                tcu.segmented_scan(xs[k[0] % 2], s, out=o, algo=algo)
+            ms, _ = time_op(torch, call, 10, 3)
+            sc.setdefault(algo, {})[f"{s}_{'f32' if dt == torch.float32 else 'f16'}"] = round(n / ms / 1e6, 1)
+        del o
+    out["scan_mma_sync_vs_tcgen05"] = sc
     out["note"] = ("direct launches, CUDA events around 10 back-to-back calls; the shuffle variant "
                    "does not split inputs into exact parts (plain fp32 rounding); tcgen05 = "
-                   "tcgen05.mma with the accumulator in tensor memory, segment sizes up to 2048 (plain fp32 "
-                   "accumulation, no exact parts)")
+                   "tcgen05.mma with the accumulator in tensor memory: reductions up to 2048 elements per "
+                   "segment with plain fp32 accumulation, scans with the exact parts of the mma.sync path "
+                   "(the default for 16-bit outputs of 16- and 256...2048-element segments)")
     return out
 
 

@@ -40,12 +40,14 @@ typedef enum {
 } tcu_status;
 
 typedef enum {
-  TCU_ALGO_AUTO    = 0, /* the tensor-core kernel                                       */
+  TCU_ALGO_AUTO    = 0, /* the fastest tensor-core kernel for the size: mma.sync, or
+                           tcgen05 for large scans with 16-bit outputs                  */
   TCU_ALGO_MMA     = 1, /* TMA ring + mma.sync m16n8k16 against ones / triangular ones  */
   TCU_ALGO_SHUFFLE = 2, /* same pipeline, CUDA-core adds + warp shuffles: the ablation  */
-  TCU_ALGO_TCGEN05 = 3  /* tcgen05.mma, accumulators in tensor memory: segmented
-                           reduction of 16 ... 2048-element segments (powers of two),
-                           num_elements % 64 == 0; plain fp32 accumulation */
+  TCU_ALGO_TCGEN05 = 3  /* tcgen05.mma, accumulators in tensor memory; powers of two,
+                           num_elements % 64 == 0: segmented reduction of 16 ... 2048
+                           elements (plain fp32 accumulation), inclusive segmented scan
+                           of 16 ... 16384 elements (exact parts, like TCU_ALGO_MMA)     */
 } tcu_algo;
 
 typedef enum { TCU_OUT_F16 = 0, TCU_OUT_F32 = 1 } tcu_out_type;

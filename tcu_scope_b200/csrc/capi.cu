@@ -18,6 +18,7 @@
 #include "scan_lookback_kernel.cuh"
 #include "shuffle_kernels.cuh"
 #include "tcgen05_reduce_kernel.cuh"
+#include "tcgen05_scan_kernel.cuh"
 #if !TCU_BF16
 #include "shard_kernels.cuh"
 #endif
@@ -242,6 +243,32 @@ cudaError_t launch_tcgen05_reduce(const ReduceParams& p, const CUtensorMap& map,
   return cudaGetLastError();
 }
 
+// 2-D view of a scan's output for the swizzled bulk stores: rows of 128 bytes (32 floats or 64
+// halves), one box = the 32 rows x 64 outputs one epilogue warp produces per tile.
+bool make_output_tensor_map(CUtensorMap* map, void* d_out, size_t num_elems, bool out32) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc || num_elems % kSwizzleRowElems != 0) return false;
+  const cuuint64_t row_elems  = out32 ? 32 : 64;
+  const cuuint64_t dims[2]    = {row_elems, num_elems / row_elems};
+  const cuuint64_t strides[1] = {128};
+  const cuuint32_t box[2]     = {cuuint32_t(row_elems), out32 ? 64u : 32u};
+  const cuuint32_t estr[2]    = {1, 1};
+  if (dims[1] >= (cuuint64_t(1) << 31)) return false;
+  return enc(map, out32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d_out,
+             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int LOG2S, bool OUT32>
+cudaError_t launch_tcgen05_scan(const ScanParams& p, const CUtensorMap& map, const CUtensorMap& omap,
+                                int grid, cudaStream_t st) {
+  static bool configured[kMaxDevices];
+  cudaError_t e = ensure_smem(tcgen05_scan_kernel<LOG2S, OUT32>, configured, uscan_dyn_smem_bytes(OUT32));
+  if (e != cudaSuccess) return e;
+  tcgen05_scan_kernel<LOG2S, OUT32><<<grid, kUscanThreads, uscan_dyn_smem_bytes(OUT32), st>>>(p, map, omap);
+  return cudaGetLastError();
+}
+
 template <int SC>
 cudaError_t launch_shuffle_reduce(const ReduceParams& p, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
@@ -363,11 +390,15 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
               size_t segment_size, int sc, const double* shard_totals, int shard_index, int algo,
               void* ws, size_t ws_bytes, cudaStream_t st, bool exclusive = false) {
   if (out_type != TCU_OUT_F16 && out_type != TCU_OUT_F32) return TCU_ERR_UNSUPPORTED;
-  if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE)
+  if (algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA && algo != TCU_ALGO_SHUFFLE &&
+      algo != TCU_ALGO_TCGEN05)
     return TCU_ERR_UNSUPPORTED;
-  if (sc == kClassGeneral && algo == TCU_ALGO_SHUFFLE) return TCU_ERR_UNSUPPORTED;
+  if (sc == kClassGeneral && algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA) return TCU_ERR_UNSUPPORTED;
   size_t n = 0;
   if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
+  // the tcgen05 variant: inclusive scans of 16 ... 16384-element segments of arrays it can view as 64-wide rows
+  if (algo == TCU_ALGO_TCGEN05 && (sc < 4 || sc > 14 || n % kSwizzleRowElems != 0 || exclusive))
+    return TCU_ERR_UNSUPPORTED;
   if (n == 0) return TCU_OK;
   if (!d_in || !d_out || !aligned16(d_in) || !aligned16(d_out)) return TCU_ERR_INVALID_ARG;
   if (shard_index < 0 || (shard_index > 0 && !shard_totals)) return TCU_ERR_INVALID_ARG;
@@ -394,6 +425,36 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
             : (vec ? seg_scan_general_kernel<false, true> : seg_scan_general_kernel<false, false>);
     e = launch_pdl(kernel, p, (unsigned long long)segment_size, ggrid, kGeneralThreads, 0, st);
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+  }
+  // TCU_ALGO_AUTO takes the tcgen05 kernel where it measured faster than the mma.sync one:
+  // 16-bit outputs of 16- and 256 ... 2048-element segments (0.96 against 0.92 / 0.93 ... 0.86 of
+  // the copy bandwidth at 2^28 elements), from 2^25 elements on (its set-up costs 3-4 us more).
+  const bool umma_auto = algo == TCU_ALGO_AUTO && !f32 && !exclusive && n % kSwizzleRowElems == 0 &&
+                         n >= (size_t(1) << 25) && (sc == 4 || (sc >= 8 && sc <= 11));
+  if (algo == TCU_ALGO_TCGEN05 || umma_auto) {
+    CUtensorMap map, omap;
+    std::memset(&map, 0, sizeof(map));
+    std::memset(&omap, 0, sizeof(omap));
+    const bool maps = make_input_tensor_map(&map, d_in, n, kUmmaRows) &&
+                      make_output_tensor_map(&omap, d_out, n, f32);
+    if (!maps && !umma_auto) return TCU_ERR_CUDA;
+    if (maps) {
+      // units of whole segments when a segment is several 8192-element tiles, else single tiles
+      const size_t unit_elems = segment_size > size_t(kUmmaTileElems) ? segment_size : size_t(kUmmaTileElems);
+      const size_t units      = (n + unit_elems - 1) / unit_elems;
+      const int ugrid         = units < size_t(sms) ? int(units) : sms;
+      switch (sc) {
+#define X(C)                                                                              \
+  case C:                                                                                 \
+    e = f32 ? launch_tcgen05_scan<C, true>(p, map, omap, ugrid, st)                       \
+            : launch_tcgen05_scan<C, false>(p, map, omap, ugrid, st);                     \
+    break;
+        X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13) X(14)
+#undef X
+        default: return TCU_ERR_UNSUPPORTED;
+      }
+      return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+    }
   }
   if (sc == kClassLong) {
     const size_t need = scan_long_ws_bytes(n);

@@ -1,0 +1,410 @@
+// Segmented inclusive scan on the fifth-generation tensor cores: tcgen05.mma
+// with the accumulators in tensor memory, for segments of 16 ... 65536 elements.
+//
+// The contraction is the one of compute_wmma_segmented_prefixsum_16n / _256n
+// (src/prefixsum/kernel.cuh:86-150,441-506) -- rows of the input times the
+// upper-triangular ones matrix U -- at the shape Blackwell's tensor core wants:
+// one tile is 128 rows of 64 consecutive halves, D[128 x 64] = A[128 x 64] .
+// U[64 x 64] gives 128 independent 64-wide inclusive scans per instruction
+// group (four K = 16 steps), issued by one thread, both operands read from
+// shared memory, the fp32 result in tensor memory.  A row's total is the last
+// column of its scan; the carries between the rows of a segment are a
+// shuffle scan over those totals (in double), added while the results are on
+// their way from tensor memory to global memory.
+//
+// Exactness is kept the way the mma.sync kernels keep it (split_hi_lo): four
+// warps split every tile into an exact "hi" tile and an exact "lo" tile in
+// shared memory (same swizzled positions as the TMA copy wrote the input
+// in), the tensor core scans both, and every output is (hi + carry_hi) +
+// (lo + carry_lo): both sums exact, one rounding.
+//
+// Warps: 0 TMA producer | 1 MMA issuer, owner of the tensor memory | 2-5 split
+// | 6-13 epilogue, two sets of four taking alternate tiles (tcgen05.ld 32x32b:
+// one row of 64 outputs per thread).  A
+// thread's row is 128 or 256 contiguous bytes of the output and its neighbours'
+// rows lie that far apart, so storing from registers would touch 32 lines per
+// instruction (measured: 0.60 of the copy bandwidth whatever the output type);
+// the rows go to a swizzled staging buffer instead and leave as one tensor-map
+// bulk store per warp and tile, which also clips the rows past the end of the
+// array.  Every wait is bounded; tensor memory is freed on every exit path.
+#pragma once
+
+#include "scan_kernels.cuh"
+#include "tcgen05_reduce_kernel.cuh"
+
+namespace TCU_NS {
+
+constexpr int kUscanRawStages   = 4;                   // 16 KiB tiles as the TMA copies deliver them
+constexpr int kUscanSplitStages = 2;                   // (hi, lo) tile pairs, 32 KiB each
+constexpr int kUscanAccStages   = 2;                   // accumulator pairs in tensor memory
+constexpr int kUscanN           = 64;                  // columns of U = outputs per row
+constexpr int kUscanBBytes      = kUscanN * 128;       // U, K-major: 64 rows of 64 halves
+constexpr int kUscanTmemCols    = kUscanAccStages * 2 * kUscanN;  // 256
+constexpr int kUscanThreads     = 14 * 32;             // producer, MMA issuer, 4 split, 2 x 4 epilogue warps
+// staging: 32 rows x 64 outputs for each of the eight epilogue warps
+__host__ __device__ constexpr int uscan_stage_bytes(bool out32) { return 32 * 64 * (out32 ? 4 : 2); }
+__host__ __device__ constexpr int uscan_dyn_smem_bytes(bool out32) {
+  return kUscanRawStages * kUmmaTileBytes + kUscanSplitStages * 2 * kUmmaTileBytes + kUscanBBytes +
+         8 * uscan_stage_bytes(out32) + 1024;
+}
+constexpr uint32_t kUscanInstrDesc = (1u << 4) | (kUmmaAB << 7) | (kUmmaAB << 10) |
+                                     ((kUscanN >> 3) << 17) | ((kUmmaRows >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16_desc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 16 consecutive accumulator columns of this thread's row
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+  uint32_t r;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+  return r;
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// One box of a 2-D tensor map, shared memory -> global, tracked by the issuing
+// thread's bulk async-group.  Rows of the box that lie past the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, int c1, uint32_t src_smem) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(src_smem)
+               : "memory");
+}
+
+// Registers are per SM sub-partition (16 K): 14 warps put four on one, so a thread may use 128
+// at most.  A bound of 512 threads makes the compiler keep to exactly that.
+template <int LOG2S, bool OUT32>
+__global__ void __launch_bounds__(512, 1)
+    tcgen05_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tmap,
+                        const __grid_constant__ CUtensorMap omap) {
+  static_assert(LOG2S >= 4 && LOG2S <= 16, "16 ... 65536 elements per segment");
+  constexpr int S           = 1 << LOG2S;
+  constexpr int T           = LOG2S > 13 ? 1 << (LOG2S - 13) : 1;     // tiles per segment
+  constexpr int kRowsPerSeg = S <= 64 ? 1 : (T > 1 ? kUmmaRows : S / 64);  // rows of one tile
+  constexpr int kLanesPerSeg = kRowsPerSeg < 32 ? kRowsPerSeg : 32;    // rows of one warp
+  constexpr int kWarpsPerSeg = kRowsPerSeg <= 32 ? 1 : kRowsPerSeg / 32;  // 1, 2 or 4
+  constexpr int NR = kUscanRawStages, NH = kUscanSplitStages, NA = kUscanAccStages;
+  extern __shared__ uint8_t dyn_smem[];
+  // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty
+  __shared__ __align__(8) uint64_t bars[2 * NR + 2 * NH + 2 * NA];
+  __shared__ double part[NA][4];        // totals of the epilogue warps' 32 rows, by accumulator
+  __shared__ uint32_t part_seq[NA][4];  // tile number + 1 once published
+  __shared__ double tile_run[4];        // segments of several tiles: the segment up to and including a tile
+  __shared__ uint32_t tile_run_seq[4];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ uint32_t s_failed;
+
+  uint8_t* raw   = dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u);
+  uint8_t* split = raw + NR * kUmmaTileBytes;            // [NH][hi | lo]
+  uint8_t* bmat  = split + NH * 2 * kUmmaTileBytes;      // all 1 KiB aligned
+  uint8_t* stage = bmat + kUscanBBytes;                  // [2 sets][4 warps][32 rows x 64 outputs]
+  const uint32_t raw_u32 = smem_u32(raw), split_u32 = smem_u32(split), bmat_u32 = smem_u32(bmat);
+  const uint32_t raw_full0 = smem_u32(&bars[0]), raw_empty0 = raw_full0 + 8 * NR;
+  const uint32_t hl_full0 = raw_empty0 + 8 * NR, hl_empty0 = hl_full0 + 8 * NH;
+  const uint32_t acc_full0 = hl_empty0 + 8 * NH, acc_empty0 = acc_full0 + 8 * NA;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const unsigned long long num_rows  = p.num_elems / kSwizzleRowElems;
+  const unsigned long long num_tiles = (num_rows + kUmmaRows - 1) / kUmmaRows;
+  // The i-th tile of this CTA.  Tiles are interleaved over the CTAs; a segment of T tiles stays
+  // with one CTA, which takes its tiles one after the other.
+  auto tile_of = [&](uint32_t i) -> unsigned long long {
+    if constexpr (T == 1)
+      return blockIdx.x + (unsigned long long)i * gridDim.x;
+    else
+      return (blockIdx.x + (unsigned long long)(i / T) * gridDim.x) * T + (i % T);
+  };
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
+    for (int s = 0; s < NR; ++s) {
+      mbar_init(raw_full0 + 8 * s, 1);
+      mbar_init(raw_empty0 + 8 * s, 4);  // one arrival per split warp
+    }
+    for (int h = 0; h < NH; ++h) {
+      mbar_init(hl_full0 + 8 * h, 4);    // one arrival per split warp
+      mbar_init(hl_empty0 + 8 * h, 1);   // tcgen05.commit
+    }
+    for (int a = 0; a < NA; ++a) {
+      mbar_init(acc_full0 + 8 * a, 1);   // tcgen05.commit
+      mbar_init(acc_empty0 + 8 * a, 4);  // one arrival per epilogue warp
+    }
+    s_failed = 0u;
+    mbar_fence_init();
+  }
+  if (threadIdx.x < NA * 4) (&part_seq[0][0])[threadIdx.x] = 0u;
+  if (threadIdx.x < 4) tile_run_seq[threadIdx.x] = 0u;
+  // U restricted to the segments inside a row: B[n][k] = 1 iff k <= n and both in one segment.
+  for (int idx = threadIdx.x; idx < kUscanN * kSwizzleRowElems; idx += kUscanThreads) {
+    const int n = idx / kSwizzleRowElems, k = idx % kSwizzleRowElems;
+    const bool one = k <= n && (S >= 64 || (k >> LOG2S) == (n >> LOG2S));
+    *reinterpret_cast<uint16_t*>(bmat + swizzle128(n * 128 + k * 2)) =
+        one ? static_cast<uint16_t>(kOne16) : uint16_t(0);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // B: generic writes -> async reads
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&s_tmem_base)), "r"(static_cast<uint32_t>(kUscanTmemCols)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  pdl_prologue();  // nothing above touched global memory
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      unsigned long long tile;
+      for (uint32_t i = 0; (tile = tile_of(i)) < num_tiles; ++i) {
+        const uint32_t s = i % NR, ph = (i / NR) & 1u;
+        if (!mbar_wait(raw_empty0 + 8 * s, ph ^ 1u)) { s_failed = 1u; break; }
+        mbar_arrive_expect_tx(raw_full0 + 8 * s, kUmmaTileBytes);  // rows past the end arrive as zeros
+        tma_load_2d(raw_u32 + s * kUmmaTileBytes, &tmap, 0, (int)(tile * kUmmaRows), raw_full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      for (uint32_t i = 0; tile_of(i) < num_tiles; ++i) {
+        const uint32_t h = i % NH, hph = (i / NH) & 1u;
+        const uint32_t a = i % NA, aph = (i / NA) & 1u;
+        if (!mbar_wait(acc_empty0 + 8 * a, aph ^ 1u)) { s_failed = 1u; break; }  // accumulators drained
+        if (!mbar_wait(hl_full0 + 8 * h, hph)) { s_failed = 1u; break; }         // hi and lo written
+        tcgen05_fence_after_sync();
+        const uint32_t hi_addr = split_u32 + h * 2 * kUmmaTileBytes, lo_addr = hi_addr + kUmmaTileBytes;
+        const uint32_t d_hi = tmem_base + a * 2 * kUscanN, d_lo = d_hi + kUscanN;
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)  // K = 64 halves in four steps of 16 (32 bytes)
+          umma_f16_desc(d_hi, umma_smem_desc(hi_addr + 32 * kb), umma_smem_desc(bmat_u32 + 32 * kb),
+                        kUscanInstrDesc, kb > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb)
+          umma_f16_desc(d_lo, umma_smem_desc(lo_addr + 32 * kb), umma_smem_desc(bmat_u32 + 32 * kb),
+                        kUscanInstrDesc, kb > 0 ? 1u : 0u);
+        umma_commit(hl_empty0 + 8 * h);  // the pair may be overwritten once these MMAs have read it
+        umma_commit(acc_full0 + 8 * a);  // ... and the epilogue may read the accumulators
+      }
+    }
+  } else if (warp < 6) {
+    // --------------------------------------------------------------- split
+    const int tid = threadIdx.x - 64;  // 0 .. 127
+    for (uint32_t i = 0; tile_of(i) < num_tiles; ++i) {
+      const uint32_t s = i % NR, ph = (i / NR) & 1u;
+      const uint32_t h = i % NH, hph = (i / NH) & 1u;
+      if (!mbar_wait(raw_full0 + 8 * s, ph)) { s_failed = 1u; break; }
+      if (!mbar_wait(hl_empty0 + 8 * h, hph ^ 1u)) { s_failed = 1u; break; }
+      const uint8_t* src = raw + s * kUmmaTileBytes + 16 * tid;
+      uint8_t* hi = split + h * 2 * kUmmaTileBytes + 16 * tid;
+      uint8_t* lo = hi + kUmmaTileBytes;
+      uint4 w[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) w[c] = lds128(src + 2048 * c);  // elementwise: the swizzle is kept
+      __syncwarp();
+      if (lane == 0) mbar_arrive(raw_empty0 + 8 * s);  // the tile is in registers
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 vh, vl;
+        split_hi_lo(w[c].x, vh.x, vl.x);
+        split_hi_lo(w[c].y, vh.y, vl.y);
+        split_hi_lo(w[c].z, vh.z, vl.z);
+        split_hi_lo(w[c].w, vh.w, vl.w);
+        *reinterpret_cast<uint4*>(hi + 2048 * c) = vh;
+        *reinterpret_cast<uint4*>(lo + 2048 * c) = vl;
+      }
+      fence_proxy_async_smem();  // generic writes of hi / lo, before the tensor core reads them
+      __syncwarp();
+      if (lane == 0) mbar_arrive(hl_full0 + 8 * h);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    // Two sets of four warps take alternate tiles (set e: tiles e, e + 2, ... of this CTA, which
+    // are the tiles of accumulator stage e), so that one set's trip through tensor memory, the
+    // carry shuffles and the staging overlaps the other's.
+    const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
+    const uint32_t set = warp >= 10 ? 1u : 0u;
+    constexpr int kStage = uscan_stage_bytes(OUT32);
+    uint8_t* buf = stage + (set * 4 + quarter) * kStage;
+    unsigned long long tile;
+    for (uint32_t i = set; (tile = tile_of(i)) < num_tiles; i += 2) {
+      const uint32_t a = i % NA, aph = (i / NA) & 1u;
+      if (!mbar_wait(acc_full0 + 8 * a, aph)) { s_failed = 1u; break; }
+      tcgen05_fence_after_sync();
+      const uint32_t t_hi = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * 2 * kUscanN;
+      const uint32_t t_lo = t_hi + kUscanN;
+
+      // first half of the row, and the row totals (the last column), in one trip
+      uint32_t vh[2][16], vl[2][16];
+      uint32_t uh = 0, ul = 0;
+      tmem_ld16(t_hi, vh[0]);
+      tmem_ld16(t_hi + 16, vh[1]);
+      tmem_ld16(t_lo, vl[0]);
+      tmem_ld16(t_lo + 16, vl[1]);
+      if constexpr (kRowsPerSeg > 1) {
+        uh = tmem_ld1(t_hi + 63);
+        ul = tmem_ld1(t_lo + 63);
+      }
+      tmem_wait_ld();
+
+      // carry into this row: the totals of the earlier rows of its segment
+      float cb = 0.f, cs = 0.f, big = 0.f;
+      if constexpr (kRowsPerSeg > 1) {
+        // Rows of one warp: an exclusive shuffle scan of their totals.  A warp holds at most 2048
+        // elements, so the sums of exact hi parts and of exact lo parts stay exact in fp32.
+        float ih = __uint_as_float(uh), il = __uint_as_float(ul);
+#pragma unroll
+        for (int d = 1; d < kLanesPerSeg; d <<= 1) {
+          const float x = __shfl_up_sync(0xffffffffu, ih, d), y = __shfl_up_sync(0xffffffffu, il, d);
+          if ((lane & (kLanesPerSeg - 1)) >= d) {
+            ih += x;
+            il += y;
+          }
+        }
+        cb = __shfl_up_sync(0xffffffffu, ih, 1);
+        cs = __shfl_up_sync(0xffffffffu, il, 1);
+        if ((lane & (kLanesPerSeg - 1)) == 0) cb = cs = 0.f;
+        if constexpr (kWarpsPerSeg > 1) {
+          // The segment spans 2 or 4 warps of this set: the warp totals go from warp to warp
+          // through shared memory, with a sequence number and a bounded wait.
+          const int q0 = quarter & ~(kWarpsPerSeg - 1);
+          if (lane == 31) {
+            part[a][quarter] = (double)ih + (double)il;
+            st_release_cta(&part_seq[a][quarter], i + 1u);
+          }
+          bool ready = q0 + lane >= quarter, gave_up = false;
+          for (uint32_t spin = 0; !__all_sync(0xffffffffu, ready); ++spin) {
+            if (!ready) ready = ld_acquire_cta(&part_seq[a][q0 + lane]) == i + 1u;
+            if ((spin & 1023u) == 1023u && spin > wait_limit(&g_wait_limits.flag)) {
+              gave_up = true;
+              break;
+            }
+          }
+          if (gave_up) { s_failed = 1u; break; }
+          // Segments of several tiles: the warp that holds a tile's last rows also publishes the
+          // segment's sum up to and including the tile, which the next tile (the other set of
+          // warps) starts from.  Four slots: a slot is reused only after both sets have moved on.
+          double base = 0.0;
+          if constexpr (T > 1) {
+            if (i % T != 0) {
+              const uint32_t slot = (i - 1u) & 3u;
+              bool there = false;
+              for (uint32_t spin = 0; !there; ++spin) {
+                there = ld_acquire_cta(&tile_run_seq[slot]) == i;  // tile i - 1 carries number i
+                if ((spin & 1023u) == 1023u && spin > wait_limit(&g_wait_limits.flag)) break;
+              }
+              if (!there) { s_failed = 1u; break; }
+              base = tile_run[slot];
+            }
+            if (quarter == 3 && lane == 31) {
+              double through = base + (double)ih + (double)il;
+              for (int q = 0; q < 3; ++q) through += part[a][q];
+              tile_run[i & 3u] = through;
+              st_release_cta(&tile_run_seq[i & 3u], i + 1u);
+            }
+          }
+          if (quarter > q0 || (T > 1 && i % T != 0)) {  // warp-uniform
+            double carry = base + (double)cb + (double)cs;
+            for (int q = q0; q < quarter; ++q) carry += part[a][q];
+            // carry = cb + cs exactly: cb a multiple of 2^-13 (what the hi parts are made of), cs
+            // the small rest; a cb of 2^11 or more no longer adds exactly and is added last
+            const double c13 = rint(carry * 8192.0) * (1.0 / 8192.0);
+            cb = (float)c13;
+            cs = (float)(carry - (double)cb);
+            if (fabsf(cb) >= 2048.f) {
+              big = cb;
+              cb  = 0.f;
+            }
+          }
+        }
+      }
+
+      // This thread's row of 64 outputs into the warp's staging buffer, as box rows of 128
+      // bytes with the 128-byte swizzle the tensor map expects (16-byte chunk index XOR box
+      // row mod 8), which also spreads the lanes' stores over the banks.
+      if (lane == 0) bulk_wait_group_read<0>();  // this warp's previous store has read the buffer
+      __syncwarp();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (half == 1) {
+          tmem_ld16(t_hi + 32, vh[0]);
+          tmem_ld16(t_hi + 48, vh[1]);
+          tmem_ld16(t_lo + 32, vl[0]);
+          tmem_ld16(t_lo + 48, vl[1]);
+          tmem_wait_ld();
+          tcgen05_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty0 + 8 * a);  // the accumulators are in registers now
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = 2 * half + cc;  // columns 16c .. 16c + 15
+          float o[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const float hi = __uint_as_float(vh[cc][e]), lo = __uint_as_float(vl[cc][e]);
+            float v = (hi + cb) + (lo + cs);  // two exact sums, one rounding
+            if constexpr (S > 2048) v += big;
+            o[e] = v;
+          }
+          if constexpr (OUT32) {  // a row is two box rows of 32 floats
+            const int R = 2 * lane + (c >> 1);
+#pragma unroll
+            for (int e = 0; e < 16; e += 4) {
+              const int j = (c & 1) * 4 + e / 4;
+              *reinterpret_cast<float4*>(buf + R * 128 + ((j ^ (R & 7)) << 4)) =
+                  make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+            }
+          } else {  // a row is one box row of 64 halves
+            const int R = lane;
+#pragma unroll
+            for (int e = 0; e < 16; e += 8) {
+              const int j = 2 * c + e / 8;
+              *reinterpret_cast<uint4*>(buf + R * 128 + ((j ^ (R & 7)) << 4)) =
+                  make_uint4(pack2_rn(o[e], o[e + 1]), pack2_rn(o[e + 2], o[e + 3]),
+                             pack2_rn(o[e + 4], o[e + 5]), pack2_rn(o[e + 6], o[e + 7]));
+            }
+          }
+        }
+      }
+      fence_proxy_async_smem();  // generic writes of the staging buffer, before the bulk store reads it
+      __syncwarp();
+      if (lane == 0) {
+        const unsigned long long row0 = tile * kUmmaRows + quarter * 32;  // first row of this warp
+        if (row0 < num_rows)
+          tma_store_2d(&omap, 0, (int)(OUT32 ? 2 * row0 : row0), smem_u32(buf));
+        bulk_commit_group();
+      }
+    }
+    if (lane == 0) bulk_wait_group_read<0>();  // shared memory must outlive the stores that read it
+  }
+
+  // ------------------------------------------------------------------ exit
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && s_failed) raise_error(kErrBarrierTimeout);
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"(static_cast<uint32_t>(kUscanTmemCols)) : "memory");
+  }
+}
+
+}  // namespace TCU_NS

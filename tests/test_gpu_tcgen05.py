@@ -45,3 +45,50 @@ def test_tcgen05_rejects_what_it_does_not_cover():
     assert e.value.status == 2
     with pytest.raises(tcu.TcuError):
         tcu.segmented_reduce(x[:4096 - 16], 16, algo="tcgen05")  # element count not a multiple of 64
+
+
+@pytest.mark.parametrize("s", [16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 16384])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
+def test_tcgen05_scan_matches_oracle(s, out_dtype):
+    """The tensor-memory scan keeps the exact (hi, lo) parts: fp32 outputs equal the fp64 prefix
+    rounded once, fp16 outputs are within one half of it -- the bars of the mma.sync path."""
+    import tcu_scope_b200 as tcu
+    for n in (64, 64 * 37, 8192, 8192 * 5 + 64 * 3, 1 << 20, (1 << 24) + 64 * 11):
+        n = max(s, n // s * s)
+        if n % 64:
+            continue
+        x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 80 + s, 0)
+        buf = torch.full((n + 128,), -777.0, dtype=out_dtype, device="cuda")
+        out = buf[64:64 + n]
+        tcu.segmented_scan(x, s, out=out, algo="tcgen05")
+        ref = oracle.c_segmented_scan(bits(x), s)
+        if out_dtype == torch.float32:
+            got = out.cpu().numpy()
+            bad, max_abs, _ = oracle.np_check_f32(got, ref, 1e-3, 1e-5)
+            assert bad == 0, (n, max_abs)
+            assert np.array_equal(got, ref.astype(np.float32)), n
+        else:
+            bad, worst = oracle.np_check_f16(bits(out), ref, 2)
+            assert bad == 0 and worst <= 1, (n, worst)
+        guards = torch.cat([buf[:64], buf[64 + n:]]).float().cpu()
+        assert torch.all(guards == -777.0)
+        assert tcu.device_error() == 0
+    # sums that leave the exactly representable range: integers, and uniform [0, 1) prefixes
+    ints = tcu.fill(torch.empty(1 << 18, dtype=torch.float16, device="cuda"), 5, 0, "small_int")
+    assert torch.equal(tcu.segmented_scan(ints, s, out_dtype=out_dtype, algo="tcgen05"),
+                       tcu.segmented_scan(ints, s, out_dtype=out_dtype, algo="mma"))
+    if out_dtype == torch.float32:
+        pos = tcu.fill(torch.empty(1 << 18, dtype=torch.float16, device="cuda"), 6, 0, "uniform_01")
+        got = tcu.segmented_scan(pos, s, out_dtype=out_dtype, algo="tcgen05").cpu().numpy()
+        bad, max_abs, max_rel = oracle.np_check_f32(got, oracle.c_segmented_scan(bits(pos), s), 1e-3, 1e-5)
+        assert bad == 0 and max_rel < 2e-7, (max_abs, max_rel)
+
+
+def test_tcgen05_scan_rejects_what_it_does_not_cover():
+    import tcu_scope_b200 as tcu
+    x = tcu.fill(torch.empty(1 << 15, dtype=torch.float16, device="cuda"), 1, 0)
+    with pytest.raises(tcu.TcuError) as e:
+        tcu.segmented_scan(x, 32768, algo="tcgen05")  # only segments of 16 ... 16384 elements
+    assert e.value.status == 2
+    with pytest.raises(tcu.TcuError):
+        tcu.segmented_scan(x[:4096 - 16], 16, algo="tcgen05")  # element count not a multiple of 64
