@@ -243,15 +243,15 @@ cudaError_t launch_tcgen05_reduce(const ReduceParams& p, const CUtensorMap& map,
   return cudaGetLastError();
 }
 
-// 2-D view of a scan's output for the swizzled bulk stores: rows of 128 bytes (32 floats or 64
-// halves), one box = the 32 rows x 64 outputs one epilogue warp produces per tile.
+// 2-D view of a scan's output for the swizzled bulk stores: rows of 64 outputs; one box = 32
+// rows x 128 bytes = what one epilogue warp stages at a time (a whole row of halves, half a
+// row of floats).
 bool make_output_tensor_map(CUtensorMap* map, void* d_out, size_t num_elems, bool out32) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc || num_elems % kSwizzleRowElems != 0) return false;
-  const cuuint64_t row_elems  = out32 ? 32 : 64;
-  const cuuint64_t dims[2]    = {row_elems, num_elems / row_elems};
-  const cuuint64_t strides[1] = {128};
-  const cuuint32_t box[2]     = {cuuint32_t(row_elems), out32 ? 64u : 32u};
+  const cuuint64_t dims[2]    = {kSwizzleRowElems, num_elems / kSwizzleRowElems};
+  const cuuint64_t strides[1] = {cuuint64_t(kSwizzleRowElems) * (out32 ? 4 : 2)};
+  const cuuint32_t box[2]     = {out32 ? 32u : 64u, 32u};
   const cuuint32_t estr[2]    = {1, 1};
   if (dims[1] >= (cuuint64_t(1) << 31)) return false;
   return enc(map, out32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d_out,
@@ -260,12 +260,11 @@ bool make_output_tensor_map(CUtensorMap* map, void* d_out, size_t num_elems, boo
 }
 
 template <int LOG2S, bool OUT32>
-cudaError_t launch_tcgen05_scan(const ScanParams& p, const CUtensorMap& map, const CUtensorMap& omap,
-                                int grid, cudaStream_t st) {
+cudaError_t launch_tcgen05_scan(const ScanParams& p, const CUtensorMap& omap, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
-  cudaError_t e = ensure_smem(tcgen05_scan_kernel<LOG2S, OUT32>, configured, uscan_dyn_smem_bytes(OUT32));
+  cudaError_t e = ensure_smem(tcgen05_scan_kernel<LOG2S, OUT32>, configured, kUscanDynSmemBytes);
   if (e != cudaSuccess) return e;
-  tcgen05_scan_kernel<LOG2S, OUT32><<<grid, kUscanThreads, uscan_dyn_smem_bytes(OUT32), st>>>(p, map, omap);
+  tcgen05_scan_kernel<LOG2S, OUT32><<<grid, kUscanThreads, kUscanDynSmemBytes, st>>>(p, omap);
   return cudaGetLastError();
 }
 
@@ -432,11 +431,9 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   const bool umma_auto = algo == TCU_ALGO_AUTO && !f32 && !exclusive && n % kSwizzleRowElems == 0 &&
                          n >= (size_t(1) << 25) && (sc == 4 || (sc >= 8 && sc <= 11));
   if (algo == TCU_ALGO_TCGEN05 || umma_auto) {
-    CUtensorMap map, omap;
-    std::memset(&map, 0, sizeof(map));
+    CUtensorMap omap;
     std::memset(&omap, 0, sizeof(omap));
-    const bool maps = make_input_tensor_map(&map, d_in, n, kUmmaRows) &&
-                      make_output_tensor_map(&omap, d_out, n, f32);
+    const bool maps = make_output_tensor_map(&omap, d_out, n, f32);
     if (!maps && !umma_auto) return TCU_ERR_CUDA;
     if (maps) {
       // units of whole segments when a segment is several 8192-element tiles, else single tiles
@@ -446,8 +443,8 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
       switch (sc) {
 #define X(C)                                                                              \
   case C:                                                                                 \
-    e = f32 ? launch_tcgen05_scan<C, true>(p, map, omap, ugrid, st)                       \
-            : launch_tcgen05_scan<C, false>(p, map, omap, ugrid, st);                     \
+    e = f32 ? launch_tcgen05_scan<C, true>(p, omap, ugrid, st)                            \
+            : launch_tcgen05_scan<C, false>(p, omap, ugrid, st);                          \
     break;
         X(4) X(5) X(6) X(7) X(8) X(9) X(10) X(11) X(12) X(13) X(14)
 #undef X

@@ -14,9 +14,9 @@
 //
 // Exactness is kept the way the mma.sync kernels keep it (split_hi_lo): four
 // warps split every tile into an exact "hi" tile and an exact "lo" tile in
-// shared memory (same swizzled positions as the TMA copy wrote the input
-// in), the tensor core scans both, and every output is (hi + carry_hi) +
-// (lo + carry_lo): both sums exact, one rounding.
+// shared memory (written in the 128-byte-swizzled K-major layout the tensor
+// core reads), the tensor core scans both, and every output is
+// (hi + carry_hi) + (lo + carry_lo): both sums exact, one rounding.
 //
 // Warps: 0 TMA producer | 1 MMA issuer, owner of the tensor memory | 2-5 split
 // | 6-13 epilogue, two sets of four taking alternate tiles (tcgen05.ld 32x32b:
@@ -41,12 +41,11 @@ constexpr int kUscanN           = 64;                  // columns of U = outputs
 constexpr int kUscanBBytes      = kUscanN * 128;       // U, K-major: 64 rows of 64 halves
 constexpr int kUscanTmemCols    = kUscanAccStages * 2 * kUscanN;  // 256
 constexpr int kUscanThreads     = 14 * 32;             // producer, MMA issuer, 4 split, 2 x 4 epilogue warps
-// staging: 32 rows x 64 outputs for each of the eight epilogue warps
-__host__ __device__ constexpr int uscan_stage_bytes(bool out32) { return 32 * 64 * (out32 ? 4 : 2); }
-__host__ __device__ constexpr int uscan_dyn_smem_bytes(bool out32) {
-  return kUscanRawStages * kUmmaTileBytes + kUscanSplitStages * 2 * kUmmaTileBytes + kUscanBBytes +
-         8 * uscan_stage_bytes(out32) + 1024;
-}
+// staging: two buffers of 32 box rows x 128 bytes for each of the eight epilogue warps
+constexpr int kUscanStageBytes   = 32 * 128;
+constexpr int kUscanDynSmemBytes = kUscanRawStages * kUmmaTileBytes +
+                                   kUscanSplitStages * 2 * kUmmaTileBytes + kUscanBBytes +
+                                   8 * 2 * kUscanStageBytes + 1024;
 constexpr uint32_t kUscanInstrDesc = (1u << 4) | (kUmmaAB << 7) | (kUmmaAB << 10) |
                                      ((kUscanN >> 3) << 17) | ((kUmmaRows >> 4) << 24);
 
@@ -92,8 +91,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, in
 // at most.  A bound of 512 threads makes the compiler keep to exactly that.
 template <int LOG2S, bool OUT32>
 __global__ void __launch_bounds__(512, 1)
-    tcgen05_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tmap,
-                        const __grid_constant__ CUtensorMap omap) {
+    tcgen05_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap omap) {
   static_assert(LOG2S >= 4 && LOG2S <= 16, "16 ... 65536 elements per segment");
   constexpr int S           = 1 << LOG2S;
   constexpr int T           = LOG2S > 13 ? 1 << (LOG2S - 13) : 1;     // tiles per segment
@@ -114,13 +112,14 @@ __global__ void __launch_bounds__(512, 1)
   uint8_t* raw   = dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u);
   uint8_t* split = raw + NR * kUmmaTileBytes;            // [NH][hi | lo]
   uint8_t* bmat  = split + NH * 2 * kUmmaTileBytes;      // all 1 KiB aligned
-  uint8_t* stage = bmat + kUscanBBytes;                  // [2 sets][4 warps][32 rows x 64 outputs]
+  uint8_t* stage = bmat + kUscanBBytes;                  // [2 sets][4 warps][2 buffers]
   const uint32_t raw_u32 = smem_u32(raw), split_u32 = smem_u32(split), bmat_u32 = smem_u32(bmat);
   const uint32_t raw_full0 = smem_u32(&bars[0]), raw_empty0 = raw_full0 + 8 * NR;
   const uint32_t hl_full0 = raw_empty0 + 8 * NR, hl_empty0 = hl_full0 + 8 * NH;
   const uint32_t acc_full0 = hl_empty0 + 8 * NH, acc_empty0 = acc_full0 + 8 * NA;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  const unsigned long long total_bytes = p.num_elems * 2ull;
   const unsigned long long num_rows  = p.num_elems / kSwizzleRowElems;
   const unsigned long long num_tiles = (num_rows + kUmmaRows - 1) / kUmmaRows;
   // The i-th tile of this CTA.  Tiles are interleaved over the CTAs; a segment of T tiles stays
@@ -133,7 +132,7 @@ __global__ void __launch_bounds__(512, 1)
   };
 
   if (threadIdx.x == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&omap)) : "memory");
     for (int s = 0; s < NR; ++s) {
       mbar_init(raw_full0 + 8 * s, 1);
       mbar_init(raw_empty0 + 8 * s, 4);  // one arrival per split warp
@@ -177,8 +176,15 @@ __global__ void __launch_bounds__(512, 1)
       for (uint32_t i = 0; (tile = tile_of(i)) < num_tiles; ++i) {
         const uint32_t s = i % NR, ph = (i / NR) & 1u;
         if (!mbar_wait(raw_empty0 + 8 * s, ph ^ 1u)) { s_failed = 1u; break; }
-        mbar_arrive_expect_tx(raw_full0 + 8 * s, kUmmaTileBytes);  // rows past the end arrive as zeros
-        tma_load_2d(raw_u32 + s * kUmmaTileBytes, &tmap, 0, (int)(tile * kUmmaRows), raw_full0 + 8 * s);
+        // A tile is 16 KiB of consecutive input: one linear copy (measured faster than the
+        // tensor-map copy; the split warps put the tile into the layout the tensor core wants).
+        // Behind the end of the array the stage keeps stale data: those rows only feed rows
+        // after them, and none of these is stored.
+        const unsigned long long off = tile * kUmmaTileBytes;
+        const unsigned long long rem = total_bytes - off;
+        const uint32_t bytes = rem < (unsigned long long)kUmmaTileBytes ? (uint32_t)rem : kUmmaTileBytes;
+        mbar_arrive_expect_tx(raw_full0 + 8 * s, bytes);
+        tma_load_1d(raw_u32 + s * kUmmaTileBytes, p.in + off, bytes, raw_full0 + 8 * s);
       }
     }
   } else if (warp == 1) {
@@ -212,12 +218,14 @@ __global__ void __launch_bounds__(512, 1)
       const uint32_t h = i % NH, hph = (i / NH) & 1u;
       if (!mbar_wait(raw_full0 + 8 * s, ph)) { s_failed = 1u; break; }
       if (!mbar_wait(hl_empty0 + 8 * h, hph ^ 1u)) { s_failed = 1u; break; }
+      // 16-byte chunk tid + 128 c of the tile: row 16 c + tid / 8, chunk tid % 8 of that row; in
+      // the hi / lo tiles it goes where the 128-byte swizzle puts it (chunk index XOR row mod 8)
       const uint8_t* src = raw + s * kUmmaTileBytes + 16 * tid;
-      uint8_t* hi = split + h * 2 * kUmmaTileBytes + 16 * tid;
+      uint8_t* hi = split + h * 2 * kUmmaTileBytes + 128 * (tid >> 3) + (((tid & 7) ^ ((tid >> 3) & 7)) << 4);
       uint8_t* lo = hi + kUmmaTileBytes;
       uint4 w[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) w[c] = lds128(src + 2048 * c);  // elementwise: the swizzle is kept
+      for (int c = 0; c < 8; ++c) w[c] = lds128(src + 2048 * c);
       __syncwarp();
       if (lane == 0) mbar_arrive(raw_empty0 + 8 * s);  // the tile is in registers
 #pragma unroll
@@ -241,8 +249,6 @@ __global__ void __launch_bounds__(512, 1)
     // carry shuffles and the staging overlaps the other's.
     const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
     const uint32_t set = warp >= 10 ? 1u : 0u;
-    constexpr int kStage = uscan_stage_bytes(OUT32);
-    uint8_t* buf = stage + (set * 4 + quarter) * kStage;
     unsigned long long tile;
     for (uint32_t i = set; (tile = tile_of(i)) < num_tiles; i += 2) {
       const uint32_t a = i % NA, aph = (i / NA) & 1u;
@@ -336,11 +342,13 @@ __global__ void __launch_bounds__(512, 1)
         }
       }
 
-      // This thread's row of 64 outputs into the warp's staging buffer, as box rows of 128
-      // bytes with the 128-byte swizzle the tensor map expects (16-byte chunk index XOR box
-      // row mod 8), which also spreads the lanes' stores over the banks.
-      if (lane == 0) bulk_wait_group_read<0>();  // this warp's previous store has read the buffer
-      __syncwarp();
+      // This thread's outputs go to the warp's staging buffers as box rows of 128 bytes with the
+      // 128-byte swizzle the tensor map expects (16-byte chunk index XOR row mod 8: the lanes'
+      // stores spread over all banks) and leave through bulk tensor stores.  Two buffers per
+      // warp: 16-bit outputs fill one per tile (a row is 128 bytes), fp32 outputs one per half
+      // row, so the copy of one buffer overlaps the filling of the other.
+      const unsigned long long row0 = tile * kUmmaRows + quarter * 32;  // first row of this warp
+      uint8_t* const bufs = stage + (set * 4 + quarter) * 2 * kUscanStageBytes;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         if (half == 1) {
@@ -353,9 +361,14 @@ __global__ void __launch_bounds__(512, 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty0 + 8 * a);  // the accumulators are in registers now
         }
+        uint8_t* const buf = bufs + (OUT32 ? half : (int)((i >> 1) & 1u)) * kUscanStageBytes;
+        if (OUT32 || half == 0) {
+          if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done
+          __syncwarp();
+        }
+        uint8_t* const my_row = buf + lane * 128;
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
-          const int c = 2 * half + cc;  // columns 16c .. 16c + 15
           float o[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
@@ -364,33 +377,31 @@ __global__ void __launch_bounds__(512, 1)
             if constexpr (S > 2048) v += big;
             o[e] = v;
           }
-          if constexpr (OUT32) {  // a row is two box rows of 32 floats
-            const int R = 2 * lane + (c >> 1);
+          if constexpr (OUT32) {  // this half row is one box row of 32 floats
 #pragma unroll
             for (int e = 0; e < 16; e += 4) {
-              const int j = (c & 1) * 4 + e / 4;
-              *reinterpret_cast<float4*>(buf + R * 128 + ((j ^ (R & 7)) << 4)) =
+              const int j = cc * 4 + e / 4;
+              *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 7)) << 4)) =
                   make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
             }
-          } else {  // a row is one box row of 64 halves
-            const int R = lane;
+          } else {  // the whole row is one box row of 64 halves
 #pragma unroll
             for (int e = 0; e < 16; e += 8) {
-              const int j = 2 * c + e / 8;
-              *reinterpret_cast<uint4*>(buf + R * 128 + ((j ^ (R & 7)) << 4)) =
+              const int j = 2 * (2 * half + cc) + e / 8;
+              *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) =
                   make_uint4(pack2_rn(o[e], o[e + 1]), pack2_rn(o[e + 2], o[e + 3]),
                              pack2_rn(o[e + 4], o[e + 5]), pack2_rn(o[e + 6], o[e + 7]));
             }
           }
         }
-      }
-      fence_proxy_async_smem();  // generic writes of the staging buffer, before the bulk store reads it
-      __syncwarp();
-      if (lane == 0) {
-        const unsigned long long row0 = tile * kUmmaRows + quarter * 32;  // first row of this warp
-        if (row0 < num_rows)
-          tma_store_2d(&omap, 0, (int)(OUT32 ? 2 * row0 : row0), smem_u32(buf));
-        bulk_commit_group();
+        if (OUT32 || half == 1) {
+          fence_proxy_async_smem();  // generic writes of the buffer, before the bulk store reads it
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < num_rows) tma_store_2d(&omap, OUT32 ? 32 * half : 0, (int)row0, smem_u32(buf));
+            bulk_commit_group();
+          }
+        }
       }
     }
     if (lane == 0) bulk_wait_group_read<0>();  // shared memory must outlive the stores that read it
