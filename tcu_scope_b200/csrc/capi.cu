@@ -159,6 +159,31 @@ cudaError_t launch_pdl(void (*kernel)(Params, unsigned long long), const Params&
   return cudaLaunchKernelEx(&cfg, kernel, p, seg_elems);
 }
 
+// Multiples of 16 up to 2048 elements that are not a power of two: rows of 16 elements, 16 rows
+// per warp step, a warp takes chunks of whole segments of about 256 rows.
+bool rows_path(size_t segment_size) { return segment_size % 16 == 0 && segment_size <= 2048; }
+
+RowsParams rows_params(const void* d_in, void* d_out, double* d_out_f64, size_t num_segments,
+                       size_t segment_size, bool out_f32, bool exclusive) {
+  RowsParams r{};
+  r.in               = static_cast<const uint8_t*>(d_in);
+  r.out              = d_out;
+  r.out_f64          = d_out_f64;
+  r.num_segments     = num_segments;
+  r.rows_per_segment = unsigned(segment_size / 16);
+  r.segs_per_chunk   = r.rows_per_segment >= 256 ? 1u : 256u / r.rows_per_segment;
+  r.out_is_f32       = out_f32;
+  r.exclusive        = exclusive;
+  return r;
+}
+
+int rows_grid(const RowsParams& r, int sms) {
+  const size_t chunks = (r.num_segments + r.segs_per_chunk - 1) / r.segs_per_chunk;
+  const size_t ctas   = (chunks + kGeneralThreads / 32 - 1) / (kGeneralThreads / 32);
+  const size_t cap    = size_t(sms) * 8;
+  return int(ctas < cap ? ctas : cap);
+}
+
 // one warp per segment, eight warps per CTA, at most eight CTAs per SM
 int general_grid(size_t num_segments, int sms) {
   const size_t ctas = (num_segments + kGeneralThreads / 32 - 1) / (kGeneralThreads / 32);
@@ -334,6 +359,12 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   int grid           = tiles < size_t(sms) ? int(tiles) : sms;
 
   cudaError_t e = cudaSuccess;
+  if (sc == kClassGeneral && rows_path(segment_size)) {
+    const RowsParams r = rows_params(d_in, d_out, d_out_f64, num_segments, segment_size,
+                                     out_type == TCU_OUT_F32, false);
+    e = launch_pdl(seg_rows_kernel<false, true>, r, rows_grid(r, sms), kGeneralThreads, 0, st);
+    return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+  }
   if (sc == kClassGeneral) {
     e = launch_pdl(segment_size % 8 == 0 ? seg_reduce_general_kernel<true>
                                          : seg_reduce_general_kernel<false>,
@@ -416,6 +447,12 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   const bool f32     = out_type == TCU_OUT_F32;
 
   cudaError_t e = cudaSuccess;
+  if (sc == kClassGeneral && rows_path(segment_size)) {
+    const RowsParams r = rows_params(d_in, d_out, nullptr, num_segments, segment_size, f32, exclusive);
+    e = f32 ? launch_pdl(seg_rows_kernel<true, true>, r, rows_grid(r, sms), kGeneralThreads, 0, st)
+            : launch_pdl(seg_rows_kernel<true, false>, r, rows_grid(r, sms), kGeneralThreads, 0, st);
+    return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+  }
   if (sc == kClassGeneral) {
     const int ggrid = general_grid(num_segments, sms);
     const bool vec  = segment_size % 4 == 0;

@@ -4,10 +4,11 @@
 // of 16" / "multiples of 256" (src/reduction/seg_wmma_16n.cu:137-172,
 // seg_wmma_256n.cu:17-27) -- and, beyond the reference, any other size from 1
 // up (tails are masked).  None of the reference's registered benchmarks uses
-// such a size, so this path is built for coverage, not for the roofline: one
-// warp per segment, data read straight from global memory, the same
-// contractions and the same exact hi/lo parts as the tiled kernels.
-// Power-of-two sizes >= 16 never come here.
+// such a size, so this path is built for coverage, not for the roofline: data
+// read straight from global memory, the same contractions and the same exact
+// hi/lo parts as the tiled kernels -- one warp per segment in general, rows of
+// 16 elements packed 16 to a step for the multiples of 16 up to 2048 (the
+// last part of this file).  Power-of-two sizes >= 16 never come here.
 //
 // kVec: every segment starts on a vector boundary (segment_size % 8 == 0 for
 // the 16-byte loads of the reduction, % 4 == 0 for the 8-byte loads and
@@ -180,6 +181,149 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
         store_masked<OUT32>(p.out, out_hi, n_hi, q0, q1, q2, q3);
       }
       carry += (double)step_h + (double)step_l;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Segment sizes that are a multiple of 16 but not a power of two, up to 2048
+// elements (48, 80, 240, 768 ...: what the reference's 16n kernels accept beyond
+// their dispatch table).  One warp per segment would leave most lanes idle on
+// the short ones, so here the array is taken as rows of 16 elements -- a
+// segment is m = S / 16 whole rows -- and a warp walks a chunk of whole
+// segments 16 rows (256 contiguous elements, one coalesced 512-byte read) at a
+// time: an all-ones MMA gives the 16 row sums, row_carries their exclusive
+// prefix inside the step, and the sums of the rows of one segment are
+// differences of those prefixes (fetched from the lane that holds the
+// segment's first row), plus what the segment brought from earlier steps.  All
+// sums are of exact hi / lo parts, as everywhere else.
+struct RowsParams {
+  const uint8_t* in;
+  void* out;
+  double* out_f64;                 // reduction only, may be null
+  unsigned long long num_segments;
+  unsigned int rows_per_segment;   // m = segment_size / 16
+  unsigned int segs_per_chunk;     // whole segments a warp takes at a time
+  int out_is_f32;
+  int exclusive;                   // scan only
+};
+
+// prefix entry of local row a (0..15) out of the per-lane values of rows g / g+8
+__device__ __forceinline__ void fetch_row_prefix(int a, float eh_lo, float el_lo, float eh_hi,
+                                                 float el_hi, float& h, float& l) {
+  const int src = 4 * (a & 7);
+  const float h0 = __shfl_sync(0xffffffffu, eh_lo, src), l0 = __shfl_sync(0xffffffffu, el_lo, src);
+  const float h1 = __shfl_sync(0xffffffffu, eh_hi, src), l1 = __shfl_sync(0xffffffffu, el_hi, src);
+  h = a < 8 ? h0 : h1;
+  l = a < 8 ? l0 : l1;
+}
+
+template <bool kScan, bool OUT32>
+__global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsParams p) {
+  pdl_prologue();
+  using Geom = ScanGeom<4>;  // linear rows: row r of a step = its elements [16r, 16r + 16)
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const unsigned long long warps = (unsigned long long)gridDim.x * (kGeneralThreads / 32);
+  const unsigned long long first =
+      (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
+  const unsigned int m = p.rows_per_segment;
+  const unsigned long long chunks = (p.num_segments + p.segs_per_chunk - 1) / p.segs_per_chunk;
+  const ScanOperands ops = make_scan_operands(lane, p.exclusive != 0);
+  const Acc zero{0.f, 0.f, 0.f, 0.f};
+  const int off_lo = Geom::lo(g, t, 0);  // bytes inside the 512-byte step
+
+  for (unsigned long long chunk = first; chunk < chunks; chunk += warps) {
+    const unsigned long long seg0 = chunk * p.segs_per_chunk;
+    const unsigned long long left = p.num_segments - seg0;
+    const unsigned int nseg = left < p.segs_per_chunk ? (unsigned int)left : p.segs_per_chunk;
+    const unsigned int rows = nseg * m;
+    const unsigned long long elem0 = seg0 * m * 16ull;
+    // this lane's two rows of the current step: position inside their segment, segment in the chunk
+    unsigned int q_lo = (unsigned)g % m, s_lo = (unsigned)g / m;
+    unsigned int q_hi = (unsigned)(g + 8) % m, s_hi = (unsigned)(g + 8) / m;
+    double open_run = 0.0;  // what the segment that is open at the start of the step has so far
+    // the loads of the next three steps are in flight while one step is worked on
+    constexpr int kAhead = 3;
+    uint2 nlo[kAhead], nhi[kAhead];
+    auto load_step = [&](unsigned int r, uint2& lo, uint2& hi) {
+      const uint8_t* src = p.in + (elem0 + 16ull * r) * 2ull;
+      lo = r + g < rows ? ldg64(src + off_lo) : make_uint2(0u, 0u);
+      hi = r + g + 8 < rows ? ldg64(src + off_lo + Geom::kHiOffset) : make_uint2(0u, 0u);
+    };
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) load_step(16u * k, nlo[k], nhi[k]);
+    for (unsigned int r0 = 0; r0 < rows; r0 += 16) {
+      const bool ok_lo = r0 + g < rows, ok_hi = r0 + g + 8 < rows;
+      const uint2 lo = nlo[0], hi = nhi[0];
+#pragma unroll
+      for (int k = 0; k + 1 < kAhead; ++k) {
+        nlo[k] = nlo[k + 1];
+        nhi[k] = nhi[k + 1];
+      }
+      load_step(r0 + 16u * kAhead, nlo[kAhead - 1], nhi[kAhead - 1]);
+      uint32_t ah[4], al[4];
+      split_hi_lo(lo.x, ah[0], al[0]);
+      split_hi_lo(hi.x, ah[1], al[1]);
+      split_hi_lo(lo.y, ah[2], al[2]);
+      split_hi_lo(hi.y, ah[3], al[3]);
+      const Acc th = mma_ones(ah, zero), tl = mma_ones(al, zero);  // d0: row g, d2: row g + 8
+      float eh_lo, el_lo, eh_hi, el_hi, step_h, step_l;
+      row_carries<16>(th, tl, g, eh_lo, el_lo, eh_hi, el_hi, step_h, step_l);
+      // sum of the rows of this row's segment that lie before it in this step
+      const bool here_lo = q_lo <= (unsigned)g, here_hi = q_hi <= (unsigned)(g + 8);
+      float bh, bl;
+      fetch_row_prefix(here_lo ? g - (int)q_lo : 0, eh_lo, el_lo, eh_hi, el_hi, bh, bl);
+      const float xh_lo = here_lo ? eh_lo - bh : eh_lo, xl_lo = here_lo ? el_lo - bl : el_lo;
+      fetch_row_prefix(here_hi ? g + 8 - (int)q_hi : 0, eh_lo, el_lo, eh_hi, el_hi, bh, bl);
+      const float xh_hi = here_hi ? eh_hi - bh : eh_hi, xl_hi = here_hi ? el_hi - bl : el_hi;
+      // ... plus what the segment brought along, if it began in an earlier step
+      const double carry_lo = (here_lo ? 0.0 : open_run) + (double)xh_lo + (double)xl_lo;
+      const double carry_hi = (here_hi ? 0.0 : open_run) + (double)xh_hi + (double)xl_hi;
+      const double incl_lo = carry_lo + (double)th.d0 + (double)tl.d0;
+      const double incl_hi = carry_hi + (double)th.d2 + (double)tl.d2;
+
+      if constexpr (!kScan) {
+        if (t == 0) {
+          if (ok_lo && q_lo == m - 1) {
+            store_seg(p.out, p.out_is_f32 != 0, seg0 + s_lo, (float)incl_lo);
+            if (p.out_f64 != nullptr) p.out_f64[seg0 + s_lo] = incl_lo;
+          }
+          if (ok_hi && q_hi == m - 1) {
+            store_seg(p.out, p.out_is_f32 != 0, seg0 + s_hi, (float)incl_hi);
+            if (p.out_f64 != nullptr) p.out_f64[seg0 + s_hi] = incl_hi;
+          }
+        }
+      } else {
+        // the carry of each row as an exact multiple of 2^-13 plus a small rest; a large one is
+        // held back and added last (see scan_step_independent)
+        const double c13_lo = rint(carry_lo * 8192.0) * (1.0 / 8192.0);
+        const double c13_hi = rint(carry_hi * 8192.0) * (1.0 / 8192.0);
+        float ch_lo = (float)c13_lo, ch_hi = (float)c13_hi;
+        const float cl_lo = (float)(carry_lo - (double)ch_lo), cl_hi = (float)(carry_hi - (double)ch_hi);
+        float big_lo = 0.f, big_hi = 0.f;
+        if (fabsf(ch_lo) >= 1024.f) { big_lo = ch_lo; ch_lo = 0.f; }
+        if (fabsf(ch_hi) >= 1024.f) { big_hi = ch_hi; ch_hi = 0.f; }
+        const Acc c_h{ch_lo, ch_lo, ch_hi, ch_hi}, c_l{cl_lo, cl_lo, cl_hi, cl_hi};
+        const Acc ha = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ua0, ops.ua1, c_h);
+        const Acc hb = mma16816(ah[0], ah[1], ah[2], ah[3], ops.ub0, ops.ub1, c_h);
+        const Acc la = mma16816(al[0], al[1], al[2], al[3], ops.ua0, ops.ua1, c_l);
+        const Acc lb = mma16816(al[0], al[1], al[2], al[3], ops.ub0, ops.ub1, c_l);
+        const unsigned long long o_lo = elem0 + 16ull * r0 + off_lo / 2;
+        if (ok_lo)
+          store4<OUT32>(p.out, o_lo, (ha.d0 + la.d0) + big_lo, (ha.d1 + la.d1) + big_lo,
+                        (hb.d0 + lb.d0) + big_lo, (hb.d1 + lb.d1) + big_lo);
+        if (ok_hi)
+          store4<OUT32>(p.out, o_lo + Geom::kHiOffset / 2, (ha.d2 + la.d2) + big_hi,
+                        (ha.d3 + la.d3) + big_hi, (hb.d2 + lb.d2) + big_hi, (hb.d3 + lb.d3) + big_hi);
+      }
+      // the segment of the step's last row stays open unless that row ends it
+      const double through15 = __shfl_sync(0xffffffffu, incl_hi, 28);
+      const unsigned int q15    = __shfl_sync(0xffffffffu, q_hi, 28);
+      open_run = q15 == m - 1 ? 0.0 : through15;
+      q_lo += 16;
+      while (q_lo >= m) { q_lo -= m; ++s_lo; }
+      q_hi += 16;
+      while (q_hi >= m) { q_hi -= m; ++s_hi; }
     }
   }
 }
