@@ -74,7 +74,7 @@ def parse_args():
                          "segment: use it with --profile reduce or --profile scan")
     ap.add_argument("--log2-elems", type=int, default=LOG2_ELEMS,
                     help="elements per GPU (default 28, the reference sweep's size)")
-    ap.add_argument("--profile", default=None, choices=["reduce", "scan", "full"],
+    ap.add_argument("--profile", default=None, choices=["reduce", "scan", "scan16", "full", "shard"],
                     help="run ONE untimed pass of the named kernels at --log2-elems and exit "
                          "(the small case an ncu capture wraps)")
     ap.add_argument("--no-extras", action="store_true",
@@ -868,6 +868,18 @@ def profile_pass(torch, tcu, args, n, json_fd):
     elif args.profile == "scan":
         for s, dt in [(16, torch.float16), (256, torch.float16), (4096, torch.float32)]:
             tcu.segmented_scan(x, s, out_dtype=dt, algo=args.algo)
+    elif args.profile == "scan16":  # the classes with 16-bit outputs that stay under 0.90
+        for s in (2048, 4096, 16384):
+            tcu.segmented_scan(x, s, out_dtype=torch.float16, algo=args.algo)
+    elif args.profile == "shard":  # the two passes of the sharded full scan, one rank
+        tcu.fill(x, 2024, 0, "uniform_01")
+        grp = tcu.PeerGroup()
+        o = torch.empty(n, dtype=torch.float32, device="cuda")
+        grp.full_scan(x, out=o)          # pass 1 asks L2 to keep 64 MiB for pass 2
+        grp.set_l2_keep_bytes(0)
+        grp.full_scan(x, out=o)          # ... and nothing
+        torch.cuda.synchronize()
+        grp.close()
     else:
         tcu.fill(x, 2024, 0, "uniform_01")
         tcu.full_reduce(x)
