@@ -80,7 +80,7 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other configurations, the e2e leg and the CPU baseline")
     args = ap.parse_args()
-    if args.algo == "tcgen05" and args.profile not in ("reduce", "scan"):
+    if args.algo == "tcgen05" and args.profile not in ("reduce", "scan", "scan16"):
         ap.error("--algo tcgen05 does not cover every size of the sweep: use it with --profile reduce "
                  "or --profile scan (the timed run reports it under ablation_tensor_core_vs_shuffle)")
     return args

@@ -1,5 +1,5 @@
 // Segmented inclusive scan on the fifth-generation tensor cores: tcgen05.mma
-// with the accumulators in tensor memory, for segments of 16 ... 65536 elements.
+// with the accumulators in tensor memory, for segments of 16 ... 16384 elements.
 //
 // The contraction is the one of compute_wmma_segmented_prefixsum_16n / _256n
 // (src/prefixsum/kernel.cuh:86-150,441-506) -- rows of the input times the
@@ -79,6 +79,19 @@ __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Packed fp32 add (two lanes of a 64-bit register pair per instruction; new with sm_100).
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 // One box of a 2-D tensor map, shared memory -> global, tracked by the issuing
 // thread's bulk async-group.  Rows of the box that lie past the tensor are not written.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, int c1, uint32_t src_smem) {
@@ -92,7 +105,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, in
 template <int LOG2S, bool OUT32>
 __global__ void __launch_bounds__(512, 1)
     tcgen05_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap omap) {
-  static_assert(LOG2S >= 4 && LOG2S <= 16, "16 ... 65536 elements per segment");
+  static_assert(LOG2S >= 4 && LOG2S <= 14, "16 ... 16384 elements per segment");
   constexpr int S           = 1 << LOG2S;
   constexpr int T           = LOG2S > 13 ? 1 << (LOG2S - 13) : 1;     // tiles per segment
   constexpr int kRowsPerSeg = S <= 64 ? 1 : (T > 1 ? kUmmaRows : S / 64);  // rows of one tile
@@ -102,10 +115,11 @@ __global__ void __launch_bounds__(512, 1)
   extern __shared__ uint8_t dyn_smem[];
   // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty
   __shared__ __align__(8) uint64_t bars[2 * NR + 2 * NH + 2 * NA];
-  __shared__ double part[NA][4];        // totals of the epilogue warps' 32 rows, by accumulator
-  __shared__ uint32_t part_seq[NA][4];  // tile number + 1 once published
-  __shared__ double tile_run[4];        // segments of several tiles: the segment up to and including a tile
-  __shared__ uint32_t tile_run_seq[4];
+  // Segments that span several epilogue warps: the sums of each quarter of a tile (32 rows),
+  // one partial per split warp, written before the tile is handed to the tensor core.  The split
+  // warps run at most NH + NA tiles ahead of the epilogue: 8 slots are never reused too early.
+  constexpr int kQSlots = 8;
+  __shared__ double qpart[kQSlots][4][4];  // [tile slot][split warp][quarter]
   __shared__ uint32_t s_tmem_base;
   __shared__ uint32_t s_failed;
 
@@ -148,8 +162,6 @@ __global__ void __launch_bounds__(512, 1)
     s_failed = 0u;
     mbar_fence_init();
   }
-  if (threadIdx.x < NA * 4) (&part_seq[0][0])[threadIdx.x] = 0u;
-  if (threadIdx.x < 4) tile_run_seq[threadIdx.x] = 0u;
   // U restricted to the segments inside a row: B[n][k] = 1 iff k <= n and both in one segment.
   for (int idx = threadIdx.x; idx < kUscanN * kSwizzleRowElems; idx += kUscanThreads) {
     const int n = idx / kSwizzleRowElems, k = idx % kSwizzleRowElems;
@@ -228,6 +240,12 @@ __global__ void __launch_bounds__(512, 1)
       for (int c = 0; c < 8; ++c) w[c] = lds128(src + 2048 * c);
       __syncwarp();
       if (lane == 0) mbar_arrive(raw_empty0 + 8 * s);  // the tile is in registers
+      // Chunks 2q and 2q + 1 of every thread lie in quarter q of the tile (rows 32q .. 32q + 31).
+      // For segments that span several epilogue warps an all-ones MMA adds this warp's part of
+      // each quarter exactly (which element lands in which row of the accumulator does not
+      // matter for a total); the epilogue warps then know what lies before their rows without
+      // waiting for one another.  All four quarters first, then one round of shuffles for all.
+      Acc qh[4], ql[4];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint4 vh, vl;
@@ -237,6 +255,32 @@ __global__ void __launch_bounds__(512, 1)
         split_hi_lo(w[c].w, vh.w, vl.w);
         *reinterpret_cast<uint4*>(hi + 2048 * c) = vh;
         *reinterpret_cast<uint4*>(lo + 2048 * c) = vl;
+        if constexpr (kWarpsPerSeg > 1) {
+          const Acc zero{0.f, 0.f, 0.f, 0.f};
+          qh[c >> 1] = mma16816(vh.x, vh.y, vh.z, vh.w, kOnesH2, kOnesH2, (c & 1) ? qh[c >> 1] : zero);
+          ql[c >> 1] = mma16816(vl.x, vl.y, vl.z, vl.w, kOnesH2, kOnesH2, (c & 1) ? ql[c >> 1] : zero);
+        }
+      }
+      if constexpr (kWarpsPerSeg > 1) {
+        float th[4], tl[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {  // rows g and g + 8, the same in every column
+          th[q] = qh[q].d0 + qh[q].d2;
+          tl[q] = ql[q].d0 + ql[q].d2;
+        }
+#pragma unroll
+        for (int off = 4; off <= 16; off <<= 1) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            th[q] += __shfl_xor_sync(0xffffffffu, th[q], off);
+            tl[q] += __shfl_xor_sync(0xffffffffu, tl[q], off);
+          }
+        }
+        if (lane < 4) {
+          const float h = lane == 0 ? th[0] : lane == 1 ? th[1] : lane == 2 ? th[2] : th[3];
+          const float l = lane == 0 ? tl[0] : lane == 1 ? tl[1] : lane == 2 ? tl[2] : tl[3];
+          qpart[i % kQSlots][warp - 2][lane] = (double)h + (double)l;
+        }
       }
       fence_proxy_async_smem();  // generic writes of hi / lo, before the tensor core reads them
       __syncwarp();
@@ -288,47 +332,19 @@ __global__ void __launch_bounds__(512, 1)
         cs = __shfl_up_sync(0xffffffffu, il, 1);
         if ((lane & (kLanesPerSeg - 1)) == 0) cb = cs = 0.f;
         if constexpr (kWarpsPerSeg > 1) {
-          // The segment spans 2 or 4 warps of this set: the warp totals go from warp to warp
-          // through shared memory, with a sequence number and a bounded wait.
+          // The segment spans 2 or 4 quarters of the tile (and, at 16384 elements, two tiles): what
+          // lies before this warp's rows is in the quarter totals the split warps left.
           const int q0 = quarter & ~(kWarpsPerSeg - 1);
-          if (lane == 31) {
-            part[a][quarter] = (double)ih + (double)il;
-            st_release_cta(&part_seq[a][quarter], i + 1u);
-          }
-          bool ready = q0 + lane >= quarter, gave_up = false;
-          for (uint32_t spin = 0; !__all_sync(0xffffffffu, ready); ++spin) {
-            if (!ready) ready = ld_acquire_cta(&part_seq[a][q0 + lane]) == i + 1u;
-            if ((spin & 1023u) == 1023u && spin > wait_limit(&g_wait_limits.flag)) {
-              gave_up = true;
-              break;
-            }
-          }
-          if (gave_up) { s_failed = 1u; break; }
-          // Segments of several tiles: the warp that holds a tile's last rows also publishes the
-          // segment's sum up to and including the tile, which the next tile (the other set of
-          // warps) starts from.  Four slots: a slot is reused only after both sets have moved on.
-          double base = 0.0;
+          double before = 0.0;
+          for (int q = q0; q < quarter; ++q)
+            for (int w = 0; w < 4; ++w) before += qpart[i % kQSlots][w][q];
           if constexpr (T > 1) {
-            if (i % T != 0) {
-              const uint32_t slot = (i - 1u) & 3u;
-              bool there = false;
-              for (uint32_t spin = 0; !there; ++spin) {
-                there = ld_acquire_cta(&tile_run_seq[slot]) == i;  // tile i - 1 carries number i
-                if ((spin & 1023u) == 1023u && spin > wait_limit(&g_wait_limits.flag)) break;
-              }
-              if (!there) { s_failed = 1u; break; }
-              base = tile_run[slot];
-            }
-            if (quarter == 3 && lane == 31) {
-              double through = base + (double)ih + (double)il;
-              for (int q = 0; q < 3; ++q) through += part[a][q];
-              tile_run[i & 3u] = through;
-              st_release_cta(&tile_run_seq[i & 3u], i + 1u);
-            }
+            if (i % T != 0)  // the segment's first tile is this CTA's previous one
+              for (int q = 0; q < 4; ++q)
+                for (int w = 0; w < 4; ++w) before += qpart[(i - 1u) % kQSlots][w][q];
           }
           if (quarter > q0 || (T > 1 && i % T != 0)) {  // warp-uniform
-            double carry = base + (double)cb + (double)cs;
-            for (int q = q0; q < quarter; ++q) carry += part[a][q];
+            const double carry = before + (double)cb + (double)cs;
             // carry = cb + cs exactly: cb a multiple of 2^-13 (what the hi parts are made of), cs
             // the small rest; a cb of 2^11 or more no longer adds exactly and is added last
             const double c13 = rint(carry * 8192.0) * (1.0 / 8192.0);
@@ -342,6 +358,8 @@ __global__ void __launch_bounds__(512, 1)
         }
       }
 
+      const float2 cb2 = make_float2(cb, cb), cs2 = make_float2(cs, cs);
+      const bool any_big = S > 2048 && __any_sync(0xffffffffu, big != 0.f);
       // This thread's outputs go to the warp's staging buffers as box rows of 128 bytes with the
       // 128-byte swizzle the tensor map expects (16-byte chunk index XOR row mod 8: the lanes'
       // stores spread over all banks) and leave through bulk tensor stores.  Two buffers per
@@ -371,11 +389,17 @@ __global__ void __launch_bounds__(512, 1)
         for (int cc = 0; cc < 2; ++cc) {
           float o[16];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float hi = __uint_as_float(vh[cc][e]), lo = __uint_as_float(vl[cc][e]);
-            float v = (hi + cb) + (lo + cs);  // two exact sums, one rounding
-            if constexpr (S > 2048) v += big;
-            o[e] = v;
+          for (int e = 0; e < 16; e += 2) {  // two outputs per packed fp32x2 instruction
+            const float2 t = add2(add2(make_float2(__uint_as_float(vh[cc][e]), __uint_as_float(vh[cc][e + 1])), cb2),
+                                  add2(make_float2(__uint_as_float(vl[cc][e]), __uint_as_float(vl[cc][e + 1])), cs2));
+            o[e]     = t.x;  // (hi + cb) + (lo + cs): two exact sums, one rounding
+            o[e + 1] = t.y;
+          }
+          if constexpr (S > 2048) {
+            if (any_big) {  // warp-uniform: only carries of 2^11 and more are held back
+#pragma unroll
+              for (int e = 0; e < 16; ++e) o[e] += big;
+            }
           }
           if constexpr (OUT32) {  // this half row is one box row of 32 floats
 #pragma unroll
