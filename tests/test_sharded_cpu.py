@@ -72,3 +72,39 @@ def test_sharded_full_ops_gloo(world):
         total, scan, (b, e) = ret[r]
         assert total == pytest.approx(ref_scan[-1], rel=1e-12)
         assert oracle.np_check_f32(scan, ref_scan[b:e])[0] == 0
+
+
+def _handle_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from tcu_scope_b200.sharded import HANDLE_BYTES, exchange_handles
+    mine = bytes([rank * 16 + k % 16 for k in range(HANDLE_BYTES)])
+    ret[rank] = exchange_handles(mine)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_setup_handles_are_gathered_in_rank_order(world):
+    """The one collective of the kernel-level exchange happens at set-up: every rank's 64-byte
+    handle, in rank order, on every rank (here over gloo; the bytes mean nothing without a GPU)."""
+    from tcu_scope_b200.sharded import HANDLE_BYTES, exchange_handles
+    port = 29900 + (os.getpid() % 1500) + world
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_handle_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    want = b"".join(bytes([r * 16 + k % 16 for k in range(HANDLE_BYTES)]) for r in range(world))
+    for r in range(world):
+        assert ret[r] == want
+    # without a process group there is nothing to exchange
+    one = bytes(range(HANDLE_BYTES))
+    assert exchange_handles(one) == one
+    with pytest.raises(ValueError):
+        exchange_handles(b"short")
