@@ -113,8 +113,8 @@ __global__ void __launch_bounds__(512, 1)
   constexpr int kWarpsPerSeg = kRowsPerSeg <= 32 ? 1 : kRowsPerSeg / 32;  // 1, 2 or 4
   constexpr int NR = kUscanRawStages, NH = kUscanSplitStages, NA = kUscanAccStages;
   extern __shared__ uint8_t dyn_smem[];
-  // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty
-  __shared__ __align__(8) uint64_t bars[2 * NR + 2 * NH + 2 * NA];
+  // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty | q_full
+  __shared__ __align__(8) uint64_t bars[2 * NR + 2 * NH + 2 * NA + 8];
   // Segments that span several epilogue warps: the sums of each quarter of a tile (32 rows),
   // one partial per split warp, written before the tile is handed to the tensor core.  The split
   // warps run at most NH + NA tiles ahead of the epilogue: 8 slots are never reused too early.
@@ -131,6 +131,7 @@ __global__ void __launch_bounds__(512, 1)
   const uint32_t raw_full0 = smem_u32(&bars[0]), raw_empty0 = raw_full0 + 8 * NR;
   const uint32_t hl_full0 = raw_empty0 + 8 * NR, hl_empty0 = hl_full0 + 8 * NH;
   const uint32_t acc_full0 = hl_empty0 + 8 * NH, acc_empty0 = acc_full0 + 8 * NA;
+  const uint32_t q_full0 = acc_empty0 + 8 * NA;  // quarter totals of a tile written (one arrival per split warp)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const unsigned long long total_bytes = p.num_elems * 2ull;
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(512, 1)
       mbar_init(acc_full0 + 8 * a, 1);   // tcgen05.commit
       mbar_init(acc_empty0 + 8 * a, 4);  // one arrival per epilogue warp
     }
+    for (int q = 0; q < 8; ++q) mbar_init(q_full0 + 8 * q, 4);
     s_failed = 0u;
     mbar_fence_init();
   }
@@ -261,6 +263,11 @@ __global__ void __launch_bounds__(512, 1)
           ql[c >> 1] = mma16816(vl.x, vl.y, vl.z, vl.w, kOnesH2, kOnesH2, (c & 1) ? ql[c >> 1] : zero);
         }
       }
+      fence_proxy_async_smem();  // generic writes of hi / lo, before the tensor core reads them
+      __syncwarp();
+      if (lane == 0) mbar_arrive(hl_full0 + 8 * h);
+      // the totals are wanted only once the tile comes back out of the tensor core: finish them
+      // after the tile has been handed on
       if constexpr (kWarpsPerSeg > 1) {
         float th[4], tl[4];
 #pragma unroll
@@ -281,10 +288,9 @@ __global__ void __launch_bounds__(512, 1)
           const float l = lane == 0 ? tl[0] : lane == 1 ? tl[1] : lane == 2 ? tl[2] : tl[3];
           qpart[i % kQSlots][warp - 2][lane] = (double)h + (double)l;
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_full0 + 8 * (i % kQSlots));
       }
-      fence_proxy_async_smem();  // generic writes of hi / lo, before the tensor core reads them
-      __syncwarp();
-      if (lane == 0) mbar_arrive(hl_full0 + 8 * h);
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -335,13 +341,16 @@ __global__ void __launch_bounds__(512, 1)
           // The segment spans 2 or 4 quarters of the tile (and, at 16384 elements, two tiles): what
           // lies before this warp's rows is in the quarter totals the split warps left.
           const int q0 = quarter & ~(kWarpsPerSeg - 1);
+          if (!mbar_wait(q_full0 + 8 * (i % kQSlots), (i / kQSlots) & 1u)) { s_failed = 1u; break; }
           double before = 0.0;
           for (int q = q0; q < quarter; ++q)
             for (int w = 0; w < 4; ++w) before += qpart[i % kQSlots][w][q];
           if constexpr (T > 1) {
-            if (i % T != 0)  // the segment's first tile is this CTA's previous one
+            if (i % T != 0) {  // the segment's first tile is this CTA's previous one
+              if (!mbar_wait(q_full0 + 8 * ((i - 1u) % kQSlots), ((i - 1u) / kQSlots) & 1u)) { s_failed = 1u; break; }
               for (int q = 0; q < 4; ++q)
                 for (int w = 0; w < 4; ++w) before += qpart[(i - 1u) % kQSlots][w][q];
+            }
           }
           if (quarter > q0 || (T > 1 && i % T != 0)) {  // warp-uniform
             const double carry = before + (double)cb + (double)cs;
