@@ -463,18 +463,19 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   // TCU_ALGO_AUTO takes the tcgen05 kernel where it measured faster than the mma.sync one:
-  // 16-bit outputs of 16- and 256 ... 2048-element segments (0.96 against 0.92 / 0.93 ... 0.86 of
-  // the copy bandwidth at 2^28 elements), from 2^25 elements on (its set-up costs 3-4 us more).
+  // 16-bit outputs of 16- and 256 ... 16384-element segments (0.95 ... 0.97 of the copy bandwidth
+  // at 2^28 elements against 0.92 / 0.93 ... 0.76), from 2^25 elements on (its set-up costs
+  // 3-4 us more).
   const bool umma_auto = algo == TCU_ALGO_AUTO && !f32 && !exclusive && n % kSwizzleRowElems == 0 &&
-                         n >= (size_t(1) << 25) && (sc == 4 || (sc >= 8 && sc <= 11));
+                         n >= (size_t(1) << 25) && (sc == 4 || (sc >= 8 && sc <= 14));
   if (algo == TCU_ALGO_TCGEN05 || umma_auto) {
     CUtensorMap omap;
     std::memset(&omap, 0, sizeof(omap));
     const bool maps = make_output_tensor_map(&omap, d_out, n, f32);
     if (!maps && !umma_auto) return TCU_ERR_CUDA;
     if (maps) {
-      // units of whole segments when a segment is several 8192-element tiles, else single tiles
-      const size_t unit_elems = segment_size > size_t(kUmmaTileElems) ? segment_size : size_t(kUmmaTileElems);
+      // work units: single tiles, or pairs of groups of four segments of more than 2048 elements
+      const size_t unit_elems = segment_size > 2048 ? 8 * segment_size : size_t(kUmmaTileElems);
       const size_t units      = (n + unit_elems - 1) / unit_elems;
       const int ugrid         = units < size_t(sms) ? int(units) : sms;
       switch (sc) {

@@ -100,26 +100,37 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, in
                : "memory");
 }
 
+// s + e = a + b exactly (Knuth's two-sum).
+__device__ __forceinline__ void two_sum(float a, float b, float& s, float& e) {
+  const float t  = __fadd_rn(a, b);
+  const float bb = __fsub_rn(t, a);
+  e = __fadd_rn(__fsub_rn(a, __fsub_rn(t, bb)), __fsub_rn(b, bb));
+  s = t;
+}
+
+// The multiple of 2^-13 nearest to x, |x| < 512: floats between 1024 and 2048 are 2^-13 apart.
+__device__ __forceinline__ float grid13(float x) { return __fsub_rn(__fadd_rn(x, 1536.f), 1536.f); }
+
 // Registers are per SM sub-partition (16 K): 14 warps put four on one, so a thread may use 128
 // at most.  A bound of 512 threads makes the compiler keep to exactly that.
 template <int LOG2S, bool OUT32>
 __global__ void __launch_bounds__(512, 1)
     tcgen05_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap omap) {
   static_assert(LOG2S >= 4 && LOG2S <= 14, "16 ... 16384 elements per segment");
-  constexpr int S           = 1 << LOG2S;
-  constexpr int T           = LOG2S > 13 ? 1 << (LOG2S - 13) : 1;     // tiles per segment
-  constexpr int kRowsPerSeg = S <= 64 ? 1 : (T > 1 ? kUmmaRows : S / 64);  // rows of one tile
-  constexpr int kLanesPerSeg = kRowsPerSeg < 32 ? kRowsPerSeg : 32;    // rows of one warp
-  constexpr int kWarpsPerSeg = kRowsPerSeg <= 32 ? 1 : kRowsPerSeg / 32;  // 1, 2 or 4
+  constexpr int S = 1 << LOG2S;
+  // Segments of more than 2048 elements (32 rows, what one epilogue warp reads of a tile) are
+  // spread over G tiles so that one warp still sees a whole segment: a group is four consecutive
+  // segments, and tile j of a group holds rows 32 j ... 32 j + 31 of each of them, one segment
+  // per quarter of the tile.  The warp of a quarter then meets its segment's rows in order, tile
+  // after tile, and carries the running total in a register: no warp waits for another.
+  constexpr int G            = LOG2S > 11 ? 1 << (LOG2S - 11) : 1;
+  constexpr int kPer         = G == 1 ? 1 : 2 * G;  // tiles of one work unit (a tile, or two groups)
+  constexpr int kRowsPerSeg  = S <= 64 ? 1 : (G > 1 ? 32 : S / 64);  // rows of a segment in a tile
+  constexpr int kLanesPerSeg = kRowsPerSeg;
   constexpr int NR = kUscanRawStages, NH = kUscanSplitStages, NA = kUscanAccStages;
   extern __shared__ uint8_t dyn_smem[];
-  // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty | q_full
-  __shared__ __align__(8) uint64_t bars[2 * NR + 2 * NH + 2 * NA + 8];
-  // Segments that span several epilogue warps: the sums of each quarter of a tile (32 rows),
-  // one partial per split warp, written before the tile is handed to the tensor core.  The split
-  // warps run at most NH + NA tiles ahead of the epilogue: 8 slots are never reused too early.
-  constexpr int kQSlots = 8;
-  __shared__ double qpart[kQSlots][4][4];  // [tile slot][split warp][quarter]
+  // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty
+  __shared__ __align__(8) uint64_t bars[2 * NR + 2 * NH + 2 * NA];
   __shared__ uint32_t s_tmem_base;
   __shared__ uint32_t s_failed;
 
@@ -131,19 +142,27 @@ __global__ void __launch_bounds__(512, 1)
   const uint32_t raw_full0 = smem_u32(&bars[0]), raw_empty0 = raw_full0 + 8 * NR;
   const uint32_t hl_full0 = raw_empty0 + 8 * NR, hl_empty0 = hl_full0 + 8 * NH;
   const uint32_t acc_full0 = hl_empty0 + 8 * NH, acc_empty0 = acc_full0 + 8 * NA;
-  const uint32_t q_full0 = acc_empty0 + 8 * NA;  // quarter totals of a tile written (one arrival per split warp)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const unsigned long long total_bytes = p.num_elems * 2ull;
-  const unsigned long long num_rows  = p.num_elems / kSwizzleRowElems;
-  const unsigned long long num_tiles = (num_rows + kUmmaRows - 1) / kUmmaRows;
-  // The i-th tile of this CTA.  Tiles are interleaved over the CTAs; a segment of T tiles stays
-  // with one CTA, which takes its tiles one after the other.
-  auto tile_of = [&](uint32_t i) -> unsigned long long {
-    if constexpr (T == 1)
-      return blockIdx.x + (unsigned long long)i * gridDim.x;
-    else
-      return (blockIdx.x + (unsigned long long)(i / T) * gridDim.x) * T + (i % T);
+  const unsigned long long num_rows = p.num_elems / kSwizzleRowElems;
+  // Work units are interleaved over the CTAs.  A unit is one tile, or, for spread segments, two
+  // groups whose tiles alternate (tile i of the unit belongs to group i % 2): the two sets of
+  // epilogue warps, which take alternate tiles, then own one group each.
+  const unsigned long long num_units =
+      G == 1 ? (num_rows + kUmmaRows - 1) / kUmmaRows
+             : (num_rows + 2ull * G * kUmmaRows - 1) / (2ull * G * kUmmaRows);
+  auto unit_of = [&](uint32_t i) -> unsigned long long {
+    return blockIdx.x + (unsigned long long)(i / kPer) * gridDim.x;
+  };
+  // First of the 32 rows that quarter q of this CTA's i-th tile holds.
+  auto quarter_row = [&](uint32_t i, int q) -> unsigned long long {
+    if constexpr (G == 1) {
+      return unit_of(i) * kUmmaRows + 32ull * q;
+    } else {
+      const uint32_t r = i % kPer;
+      const unsigned long long group = 2ull * unit_of(i) + (r & 1u);
+      return (group * 4ull + q) * (32ull * G) + 32ull * (r >> 1);
+    }
   };
 
   if (threadIdx.x == 0) {
@@ -160,7 +179,6 @@ __global__ void __launch_bounds__(512, 1)
       mbar_init(acc_full0 + 8 * a, 1);   // tcgen05.commit
       mbar_init(acc_empty0 + 8 * a, 4);  // one arrival per epilogue warp
     }
-    for (int q = 0; q < 8; ++q) mbar_init(q_full0 + 8 * q, 4);
     s_failed = 0u;
     mbar_fence_init();
   }
@@ -186,25 +204,42 @@ __global__ void __launch_bounds__(512, 1)
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      unsigned long long tile;
-      for (uint32_t i = 0; (tile = tile_of(i)) < num_tiles; ++i) {
+      for (uint32_t i = 0; unit_of(i) < num_units; ++i) {
         const uint32_t s = i % NR, ph = (i / NR) & 1u;
         if (!mbar_wait(raw_empty0 + 8 * s, ph ^ 1u)) { s_failed = 1u; break; }
-        // A tile is 16 KiB of consecutive input: one linear copy (measured faster than the
-        // tensor-map copy; the split warps put the tile into the layout the tensor core wants).
-        // Behind the end of the array the stage keeps stale data: those rows only feed rows
-        // after them, and none of these is stored.
-        const unsigned long long off = tile * kUmmaTileBytes;
-        const unsigned long long rem = total_bytes - off;
-        const uint32_t bytes = rem < (unsigned long long)kUmmaTileBytes ? (uint32_t)rem : kUmmaTileBytes;
-        mbar_arrive_expect_tx(raw_full0 + 8 * s, bytes);
-        tma_load_1d(raw_u32 + s * kUmmaTileBytes, p.in + off, bytes, raw_full0 + 8 * s);
+        // Linear copies (measured faster than a tensor-map copy; the split warps put the tile into
+        // the layout the tensor core wants): 16 KiB of consecutive input, or one piece of 4 KiB
+        // per quarter.  Behind the end of the array the stage keeps stale data: those rows only
+        // feed rows after them, and none of these is stored.
+        const uint32_t dst = raw_u32 + s * kUmmaTileBytes, bar = raw_full0 + 8 * s;
+        if constexpr (G == 1) {
+          const unsigned long long row = quarter_row(i, 0);
+          const unsigned long long rem = (num_rows - row) * 128ull;
+          const uint32_t bytes = rem < (unsigned long long)kUmmaTileBytes ? (uint32_t)rem : kUmmaTileBytes;
+          mbar_arrive_expect_tx(bar, bytes);
+          tma_load_1d(dst, p.in + row * 128ull, bytes, bar);
+        } else {
+          // whole segments only: a quarter's 32 rows are all inside the array or all outside
+          uint32_t pieces = 0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) pieces += quarter_row(i, q) < num_rows ? 1u : 0u;
+          if (pieces == 0) {
+            mbar_arrive(bar);
+          } else {
+            mbar_arrive_expect_tx(bar, pieces * 4096u);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const unsigned long long row = quarter_row(i, q);
+              if (row < num_rows) tma_load_1d(dst + q * 4096u, p.in + row * 128ull, 4096u, bar);
+            }
+          }
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      for (uint32_t i = 0; tile_of(i) < num_tiles; ++i) {
+      for (uint32_t i = 0; unit_of(i) < num_units; ++i) {
         const uint32_t h = i % NH, hph = (i / NH) & 1u;
         const uint32_t a = i % NA, aph = (i / NA) & 1u;
         if (!mbar_wait(acc_empty0 + 8 * a, aph ^ 1u)) { s_failed = 1u; break; }  // accumulators drained
@@ -227,7 +262,7 @@ __global__ void __launch_bounds__(512, 1)
   } else if (warp < 6) {
     // --------------------------------------------------------------- split
     const int tid = threadIdx.x - 64;  // 0 .. 127
-    for (uint32_t i = 0; tile_of(i) < num_tiles; ++i) {
+    for (uint32_t i = 0; unit_of(i) < num_units; ++i) {
       const uint32_t s = i % NR, ph = (i / NR) & 1u;
       const uint32_t h = i % NH, hph = (i / NH) & 1u;
       if (!mbar_wait(raw_full0 + 8 * s, ph)) { s_failed = 1u; break; }
@@ -242,12 +277,6 @@ __global__ void __launch_bounds__(512, 1)
       for (int c = 0; c < 8; ++c) w[c] = lds128(src + 2048 * c);
       __syncwarp();
       if (lane == 0) mbar_arrive(raw_empty0 + 8 * s);  // the tile is in registers
-      // Chunks 2q and 2q + 1 of every thread lie in quarter q of the tile (rows 32q .. 32q + 31).
-      // For segments that span several epilogue warps an all-ones MMA adds this warp's part of
-      // each quarter exactly (which element lands in which row of the accumulator does not
-      // matter for a total); the epilogue warps then know what lies before their rows without
-      // waiting for one another.  All four quarters first, then one round of shuffles for all.
-      Acc qh[4], ql[4];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint4 vh, vl;
@@ -257,40 +286,10 @@ __global__ void __launch_bounds__(512, 1)
         split_hi_lo(w[c].w, vh.w, vl.w);
         *reinterpret_cast<uint4*>(hi + 2048 * c) = vh;
         *reinterpret_cast<uint4*>(lo + 2048 * c) = vl;
-        if constexpr (kWarpsPerSeg > 1) {
-          const Acc zero{0.f, 0.f, 0.f, 0.f};
-          qh[c >> 1] = mma16816(vh.x, vh.y, vh.z, vh.w, kOnesH2, kOnesH2, (c & 1) ? qh[c >> 1] : zero);
-          ql[c >> 1] = mma16816(vl.x, vl.y, vl.z, vl.w, kOnesH2, kOnesH2, (c & 1) ? ql[c >> 1] : zero);
-        }
       }
       fence_proxy_async_smem();  // generic writes of hi / lo, before the tensor core reads them
       __syncwarp();
       if (lane == 0) mbar_arrive(hl_full0 + 8 * h);
-      // the totals are wanted only once the tile comes back out of the tensor core: finish them
-      // after the tile has been handed on
-      if constexpr (kWarpsPerSeg > 1) {
-        float th[4], tl[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {  // rows g and g + 8, the same in every column
-          th[q] = qh[q].d0 + qh[q].d2;
-          tl[q] = ql[q].d0 + ql[q].d2;
-        }
-#pragma unroll
-        for (int off = 4; off <= 16; off <<= 1) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            th[q] += __shfl_xor_sync(0xffffffffu, th[q], off);
-            tl[q] += __shfl_xor_sync(0xffffffffu, tl[q], off);
-          }
-        }
-        if (lane < 4) {
-          const float h = lane == 0 ? th[0] : lane == 1 ? th[1] : lane == 2 ? th[2] : th[3];
-          const float l = lane == 0 ? tl[0] : lane == 1 ? tl[1] : lane == 2 ? tl[2] : tl[3];
-          qpart[i % kQSlots][warp - 2][lane] = (double)h + (double)l;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(q_full0 + 8 * (i % kQSlots));
-      }
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -299,8 +298,8 @@ __global__ void __launch_bounds__(512, 1)
     // carry shuffles and the staging overlaps the other's.
     const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
     const uint32_t set = warp >= 10 ? 1u : 0u;
-    unsigned long long tile;
-    for (uint32_t i = set; (tile = tile_of(i)) < num_tiles; i += 2) {
+    float rh = 0.f, rl = 0.f;  // spread segments: the total of the segment's rows in the group's earlier tiles
+    for (uint32_t i = set; unit_of(i) < num_units; i += 2) {
       const uint32_t a = i % NA, aph = (i / NA) & 1u;
       if (!mbar_wait(acc_full0 + 8 * a, aph)) { s_failed = 1u; break; }
       tcgen05_fence_after_sync();
@@ -337,33 +336,36 @@ __global__ void __launch_bounds__(512, 1)
         cb = __shfl_up_sync(0xffffffffu, ih, 1);
         cs = __shfl_up_sync(0xffffffffu, il, 1);
         if ((lane & (kLanesPerSeg - 1)) == 0) cb = cs = 0.f;
-        if constexpr (kWarpsPerSeg > 1) {
-          // The segment spans 2 or 4 quarters of the tile (and, at 16384 elements, two tiles): what
-          // lies before this warp's rows is in the quarter totals the split warps left.
-          const int q0 = quarter & ~(kWarpsPerSeg - 1);
-          if (!mbar_wait(q_full0 + 8 * (i % kQSlots), (i / kQSlots) & 1u)) { s_failed = 1u; break; }
-          double before = 0.0;
-          for (int q = q0; q < quarter; ++q)
-            for (int w = 0; w < 4; ++w) before += qpart[i % kQSlots][w][q];
-          if constexpr (T > 1) {
-            if (i % T != 0) {  // the segment's first tile is this CTA's previous one
-              if (!mbar_wait(q_full0 + 8 * ((i - 1u) % kQSlots), ((i - 1u) / kQSlots) & 1u)) { s_failed = 1u; break; }
-              for (int q = 0; q < 4; ++q)
-                for (int w = 0; w < 4; ++w) before += qpart[(i - 1u) % kQSlots][w][q];
-            }
-          }
-          if (quarter > q0 || (T > 1 && i % T != 0)) {  // warp-uniform
-            const double carry = before + (double)cb + (double)cs;
-            // carry = cb + cs exactly: cb a multiple of 2^-13 (what the hi parts are made of), cs
-            // the small rest; a cb of 2^11 or more no longer adds exactly and is added last
-            const double c13 = rint(carry * 8192.0) * (1.0 / 8192.0);
-            cb = (float)c13;
-            cs = (float)(carry - (double)cb);
-            if (fabsf(cb) >= 2048.f) {
-              big = cb;
+        if constexpr (G > 1) {
+          // The segment goes on over the group's tiles.  What this warp met of it so far is kept
+          // as two floats (double arithmetic measured 7 % of the kernel's time here): rh, a sum of
+          // hi parts and so a multiple of 2^-13, exact below 2^11, and rl, the sum of the lo parts
+          // less its multiples of 2^-13, which move over to rh; beyond 2^11 rl also takes what
+          // the additions to rh round off, so that rh + rl keeps 48 bits.
+          const float th = __shfl_sync(0xffffffffu, ih, 31), tl = __shfl_sync(0xffffffffu, il, 31);
+          if ((i % kPer) < 2u) {  // the group's first tile: the segment begins here
+            rh = 0.f;
+            rl = 0.f;
+          } else {
+            const float ns = rl + cs;
+            const float m  = grid13(ns);
+            cs = ns - m;
+            float nb, e;
+            two_sum(rh, cb + m, nb, e);
+            if (fabsf(nb) >= 2048.f) {  // no longer adds exactly: held back and added last
+              cs += e;
+              big = nb;
               cb  = 0.f;
+            } else {
+              cb = nb;
             }
           }
+          float e1, e2;
+          two_sum(rh, th, rh, e1);
+          rl += tl + e1;
+          const float m = grid13(rl);
+          two_sum(rh, m, rh, e2);
+          rl = (rl - m) + e2;
         }
       }
 
@@ -374,7 +376,7 @@ __global__ void __launch_bounds__(512, 1)
       // stores spread over all banks) and leave through bulk tensor stores.  Two buffers per
       // warp: 16-bit outputs fill one per tile (a row is 128 bytes), fp32 outputs one per half
       // row, so the copy of one buffer overlaps the filling of the other.
-      const unsigned long long row0 = tile * kUmmaRows + quarter * 32;  // first row of this warp
+      const unsigned long long row0 = quarter_row(i, quarter);  // first row of this warp
       uint8_t* const bufs = stage + (set * 4 + quarter) * 2 * kUscanStageBytes;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {

@@ -53,7 +53,8 @@ def test_tcgen05_scan_matches_oracle(s, out_dtype):
     """The tensor-memory scan keeps the exact (hi, lo) parts: fp32 outputs equal the fp64 prefix
     rounded once, fp16 outputs are within one half of it -- the bars of the mma.sync path."""
     import tcu_scope_b200 as tcu
-    for n in (64, 64 * 37, 8192, 8192 * 5 + 64 * 3, 1 << 20, (1 << 24) + 64 * 11):
+    # ... and, for segments spread over several tiles, groups of four segments that are not full
+    for n in (64, 64 * 37, 8192, 8192 * 5 + 64 * 3, 1 << 20, (1 << 24) + 64 * 11, 7 * s, 1197 * s):
         n = max(s, n // s * s)
         if n % 64:
             continue
