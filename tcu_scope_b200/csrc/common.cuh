@@ -300,4 +300,15 @@ __device__ __forceinline__ void split_hi_lo(uint32_t x, uint32_t& hi, uint32_t& 
   asm("sub.rn." TCU_X2 " %0, %1, %2;" : "=r"(lo) : "r"(x), "r"(hi));
 }
 
+// s + e = a + b exactly (Knuth's two-sum).
+__device__ __forceinline__ void two_sum(float a, float b, float& s, float& e) {
+  const float t  = __fadd_rn(a, b);
+  const float bb = __fsub_rn(t, a);
+  e = __fadd_rn(__fsub_rn(a, __fsub_rn(t, bb)), __fsub_rn(b, bb));
+  s = t;
+}
+
+// The multiple of 2^-13 nearest to x, |x| < 512: floats between 1024 and 2048 are 2^-13 apart.
+__device__ __forceinline__ float grid13(float x) { return __fsub_rn(__fadd_rn(x, 1536.f), 1536.f); }
+
 }  // namespace TCU_NS

@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   __shared__ __align__(8) uint64_t bars[2 * NA + 2 * NB + 3 * NQ];
   __shared__ unsigned long long slot_tile[NQ];
   __shared__ float2 part[NQ][kConsumerWarps];      // slice totals (exact hi, lo)
-  __shared__ double tile_excl[NQ];                 // exclusive prefix of the tile in its segment
+  __shared__ float2 xcarry[NQ][kConsumerWarps];    // everything before a slice in its segment: (coarse, rest)
   __shared__ uint32_t s_abort, s_end_index;
 
   // 1 KiB-aligned rings: the swizzle pattern repeats every 1024 bytes
@@ -258,9 +258,15 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       const uint32_t q = i % NQ, ph = (i / NQ) & 1u;
       if (!mbar_wait_or_stop(p1done0 + 8 * q, ph, abort_flag, end_index, i)) break;
       const unsigned long long tile = slot_tile[q];
-      double agg = 0.0;
+      // the tile's total, and in lane w what the tile holds before slice w (double arithmetic is
+      // slow on this part: it is done here, once per tile, not in the eight pass-2 warps)
+      double agg = 0.0, pre = 0.0;
 #pragma unroll
-      for (int w = 0; w < kConsumerWarps; ++w) agg += (double)part[q][w].x + (double)part[q][w].y;
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const double v = (double)part[q][w].x + (double)part[q][w].y;
+        if (w < lane) pre += v;
+        agg += v;
+      }
       // Two levels: tiles inside a block of kBlockTiles tiles, then whole blocks
       // (block b of a segment = tiles [seg_first + b*32, +32)).  A walk is at
       // most one window inside the block plus about one window over blocks,
@@ -302,10 +308,16 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
       // the last tile of a block publishes the prefix through the block
       if (closes_block && lane == 0)
         status_store(p.block_status + blk_base + blk, excl + agg, kStateInclusive);
-      if (lane == 0) {
-        tile_excl[q] = excl;
-        mbar_arrive(resolved0 + 8 * q);  // release: tile_excl is visible to the waiters
+      // Everything before slice w, as two floats: xh a multiple of 2^-13 (what the hi parts are
+      // made of), xl the small rest.
+      if (lane < kConsumerWarps) {
+        const double carry    = excl + pre;
+        const double carry_hi = rint(carry * 8192.0) * (1.0 / 8192.0);
+        const float xh = (float)carry_hi;
+        xcarry[q][lane] = make_float2(xh, (float)(carry - (double)xh));
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(resolved0 + 8 * q);  // release: xcarry is visible to the waiters
     }
     return;
   }
@@ -372,21 +384,16 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
   auto pass2 = [&](uint32_t k) -> bool {
     const uint32_t b = k % NB, q = k % NQ;
     // producer B loads the tile only after its look-back; the second wait returns at once
-    // and makes tile_excl visible to this warp as well
+    // and makes xcarry visible to this warp as well
     if (!mbar_wait_or_stop(full_b0 + 8 * b, (k / NB) & 1u, abort_flag, end_index, k)) return false;
     if (!mbar_wait_or_stop(resolved0 + 8 * q, (k / NQ) & 1u, abort_flag, end_index, k)) return false;
     const unsigned long long tile = slot_tile[q];
     const SliceView v = slice_view(ring_b + b * kTileBytes, tile);
-    double carry = tile_excl[q];
-    for (int w = 0; w < cw; ++w) carry += (double)part[q][w].x + (double)part[q][w].y;
-    // Everything before this slice, as two floats: xh a multiple of 2^-13 (what the
-    // hi parts are made of), xl the small rest.  While xh is below 2^10 it rides
-    // through the MMAs' accumulator operand with the row carries and every sum
-    // stays exact; a larger one would push the row sums out of the accumulator's
-    // 24 bits, so it is held back and added to each output last.
-    const double carry_hi = rint(carry * 8192.0) * (1.0 / 8192.0);
-    const float xh = (float)carry_hi;
-    const float xl = (float)(carry - (double)xh);
+    // Everything before this slice, as the look-back warp left it.  While xh is below 2^10 it
+    // rides through the MMAs' accumulator operand with the row carries and every sum stays
+    // exact; a larger one would push the row sums out of the accumulator's 24 bits, so it is
+    // held back and added to each output last.
+    const float xh = xcarry[q][cw].x, xl = xcarry[q][cw].y;
     const bool fold = fabsf(xh) < 1024.f;
     const float xf = fold ? xh : 0.f, big = fold ? 0.f : xh;
     if (v.valid_bytes > 0) {
@@ -422,7 +429,7 @@ __global__ void __launch_bounds__(kLookbackThreads, kLookbackCtasPerSm)
     __syncwarp();
     if (lane == 0) {
       mbar_arrive(empty_b0 + 8 * b);
-      mbar_arrive(qfree0 + 8 * q);  // slot_tile, part, carries and tile_excl of the slot are free
+      mbar_arrive(qfree0 + 8 * q);  // slot_tile, part, carries and xcarry of the slot are free
     }
     return true;
   };

@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) shard_reduce_kernel(const ShardPa
 // totals, slice totals meet in shared memory once per tile); the carry from
 // everything earlier rides through the accumulators while it is small and is
 // added last once it is not (scan_step_independent).  The carry across tiles
-// is a double every warp keeps for itself.  The consumer warps meet at one
+// is a compensated pair of floats every warp keeps for itself.  The consumer warps meet at one
 // barrier per tile: with fp32 outputs, two thirds of the traffic are writes,
 // and they reach HBM in better order when a CTA's warps store the same tile
 // together (point-to-point hand-offs measured 3 % slower, 16 warps on half
@@ -283,6 +283,10 @@ __global__ void __launch_bounds__(kThreads, 1) shard_scan_kernel(const ShardPara
     if (p.x.rank > 0) run = wait_totals(p.x, __ldcg(p.x.seq_counter), p.x.rank, lane);
     run += sum_cta_totals(p.cta_total, blockIdx.x, lane);
   }
+  // ... kept from here on as two floats (double arithmetic measured slow on this part): rh a
+  // multiple of 2^-13 like the hi parts, rl the rest
+  float rh = (float)(rint(run * 8192.0) * (1.0 / 8192.0));
+  float rl = (float)(run - (double)rh);
 
   uint32_t i = 0;
   for (unsigned long long tile = tile_begin; tile < tile_end; ++tile, ++i) {
@@ -315,22 +319,39 @@ __global__ void __launch_bounds__(kThreads, 1) shard_scan_kernel(const ShardPara
     row_carries<16>(tot_h, tot_l, g, ch_lo, cl_lo, ch_hi, cl_hi, slice_h, slice_l);
     if (lane == 0) part[i & 1][warp] = make_float2(active ? slice_h : 0.f, active ? slice_l : 0.f);
     consumer_sync();  // one meeting per tile; part[] is double-buffered across it
-    double carry = run;
+    // One chain of exact additions over the tile's slices: this warp's carry on the way, the
+    // run's new total at the end.  (ch, cl) is a compensated pair: ch the sum of the hi parts,
+    // cl the lo parts plus whatever an addition to ch rounded off (nothing below 2^11).
+    float ch = rh, cl = rl, wh = rh, wl = rl;
 #pragma unroll
     for (int w = 0; w < kConsumerWarps; ++w) {
+      if (w == warp) {
+        wh = ch;
+        wl = cl;
+      }
       const float2 pr = part[i & 1][w];
-      const double v  = (double)pr.x + (double)pr.y;
-      if (w < warp) carry += v;
-      run += v;
+      float e;
+      two_sum(ch, pr.x, ch, e);
+      cl += pr.y + e;
+    }
+    {  // multiples of 2^-13 that the lo parts have added up to move over to the coarse part
+      const float m = grid13(cl);
+      float e;
+      two_sum(ch, m, rh, e);
+      rl = (cl - m) + e;
     }
     if (!active) continue;
 
     // everything before this slice as two floats: xh a multiple of 2^-13, xl the
     // rest.  Below 2^10, xh rides through the accumulators with the row carries
     // (every sum stays exact); above, it is added to each output last.
-    const double carry_hi = rint(carry * 8192.0) * (1.0 / 8192.0);
-    const float xh = (float)carry_hi;
-    const float xl = (float)(carry - (double)xh);
+    float xh, xl;
+    {
+      const float m = grid13(wl);
+      float e;
+      two_sum(wh, m, xh, e);
+      xl = (wl - m) + e;
+    }
     const bool fold = fabsf(xh) < 1024.f;
     const float xf = fold ? xh : 0.f, big = fold ? 0.f : xh;
     RowCarry rc{ch_lo + xf, cl_lo + xl, ch_hi + xf, cl_hi + xl};

@@ -100,17 +100,6 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, in
                : "memory");
 }
 
-// s + e = a + b exactly (Knuth's two-sum).
-__device__ __forceinline__ void two_sum(float a, float b, float& s, float& e) {
-  const float t  = __fadd_rn(a, b);
-  const float bb = __fsub_rn(t, a);
-  e = __fadd_rn(__fsub_rn(a, __fsub_rn(t, bb)), __fsub_rn(b, bb));
-  s = t;
-}
-
-// The multiple of 2^-13 nearest to x, |x| < 512: floats between 1024 and 2048 are 2^-13 apart.
-__device__ __forceinline__ float grid13(float x) { return __fsub_rn(__fadd_rn(x, 1536.f), 1536.f); }
-
 // Registers are per SM sub-partition (16 K): 14 warps put four on one, so a thread may use 128
 // at most.  A bound of 512 threads makes the compiler keep to exactly that.
 template <int LOG2S, bool OUT32>
