@@ -74,7 +74,7 @@ def parse_args():
                          "segment: use it with --profile reduce or --profile scan")
     ap.add_argument("--log2-elems", type=int, default=LOG2_ELEMS,
                     help="elements per GPU (default 28, the reference sweep's size)")
-    ap.add_argument("--profile", default=None, choices=["reduce", "scan", "scan16", "full", "shard"],
+    ap.add_argument("--profile", default=None, choices=["reduce", "scan", "scan16", "full", "shard", "general"],
                     help="run ONE untimed pass of the named kernels at --log2-elems and exit "
                          "(the small case an ncu capture wraps)")
     ap.add_argument("--no-extras", action="store_true",
@@ -871,6 +871,11 @@ def profile_pass(torch, tcu, args, n, json_fd):
     elif args.profile == "scan16":  # the classes with 16-bit outputs that stay under 0.90
         for s in (2048, 4096, 16384):
             tcu.segmented_scan(x, s, out_dtype=torch.float16, algo=args.algo)
+    elif args.profile == "general":  # a segment size that is a multiple of 16 but no power of two
+        x = x[:n // 48 * 48]
+        tcu.segmented_reduce(x, 48)
+        tcu.segmented_scan(x, 48, out_dtype=torch.float32)
+        tcu.segmented_scan(x, 48, out_dtype=torch.float16)
     elif args.profile == "shard":  # the two passes of the sharded full scan, one rank
         tcu.fill(x, 2024, 0, "uniform_01")
         grp = tcu.PeerGroup()

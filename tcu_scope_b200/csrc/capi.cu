@@ -171,7 +171,9 @@ RowsParams rows_params(const void* d_in, void* d_out, double* d_out_f64, size_t 
   r.out_f64          = d_out_f64;
   r.num_segments     = num_segments;
   r.rows_per_segment = unsigned(segment_size / 16);
-  r.segs_per_chunk   = r.rows_per_segment >= 256 ? 1u : 256u / r.rows_per_segment;
+  r.segment_bytes    = unsigned(segment_size * 2);
+  // (the reduction takes any multiple of 8 elements and does not use the chunks)
+  r.segs_per_chunk   = r.rows_per_segment >= 256 || r.rows_per_segment == 0 ? 1u : 256u / r.rows_per_segment;
   r.out_is_f32       = out_f32;
   r.exclusive        = exclusive;
   return r;
@@ -359,10 +361,12 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   int grid           = tiles < size_t(sms) ? int(tiles) : sms;
 
   cudaError_t e = cudaSuccess;
-  if (sc == kClassGeneral && rows_path(segment_size)) {
+  if (sc == kClassGeneral && segment_size % 8 == 0 && segment_size <= 2048) {
     const RowsParams r = rows_params(d_in, d_out, d_out_f64, num_segments, segment_size,
                                      out_type == TCU_OUT_F32, false);
-    e = launch_pdl(seg_rows_kernel<false, true>, r, rows_grid(r, sms), kGeneralThreads, 0, st);
+    const size_t ctas = ((num_segments + 15) / 16 + kGeneralThreads / 32 - 1) / (kGeneralThreads / 32);
+    const size_t cap  = size_t(sms) * 8;
+    e = launch_pdl(seg_rowsum_kernel, r, int(ctas < cap ? ctas : cap), kGeneralThreads, 0, st);
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   if (sc == kClassGeneral) {
@@ -449,8 +453,8 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   cudaError_t e = cudaSuccess;
   if (sc == kClassGeneral && rows_path(segment_size)) {
     const RowsParams r = rows_params(d_in, d_out, nullptr, num_segments, segment_size, f32, exclusive);
-    e = f32 ? launch_pdl(seg_rows_kernel<true, true>, r, rows_grid(r, sms), kGeneralThreads, 0, st)
-            : launch_pdl(seg_rows_kernel<true, false>, r, rows_grid(r, sms), kGeneralThreads, 0, st);
+    e = f32 ? launch_pdl(seg_rows_kernel<true>, r, rows_grid(r, sms), kGeneralThreads, 0, st)
+            : launch_pdl(seg_rows_kernel<false>, r, rows_grid(r, sms), kGeneralThreads, 0, st);
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   if (sc == kClassGeneral) {

@@ -308,7 +308,23 @@ __device__ __forceinline__ void two_sum(float a, float b, float& s, float& e) {
   s = t;
 }
 
+// (h, l) += (bh, bl) for compensated pairs: l also takes what the addition to h rounds off.
+__device__ __forceinline__ void pair_add(float& h, float& l, float bh, float bl) {
+  float e;
+  two_sum(h, bh, h, e);
+  l += bl + e;
+}
+
 // The multiple of 2^-13 nearest to x, |x| < 512: floats between 1024 and 2048 are 2^-13 apart.
 __device__ __forceinline__ float grid13(float x) { return __fsub_rn(__fadd_rn(x, 1536.f), 1536.f); }
+
+// Moves the multiples of 2^-13 that l has added up to over to h; h + l stays what it was (for
+// a large l the move is no longer to the grid, but still exact).
+__device__ __forceinline__ void pair_renorm(float& h, float& l) {
+  const float m = grid13(l);
+  float e;
+  two_sum(h, m, h, e);
+  l = __fsub_rn(l, m) + e;
+}
 
 }  // namespace TCU_NS

@@ -54,7 +54,8 @@ __device__ __forceinline__ void store_masked(void* out, unsigned long long idx, 
 // Each warp walks whole segments.  Per step a lane takes 16 bytes (8 halves);
 // the four registers are the A fragment of one MMA against all-ones, so every
 // element lands in exactly one row sum, whichever row that is.  Row sums of
-// the exact hi and lo parts are flushed into doubles before they can round.
+// the exact hi and lo parts are flushed into a compensated pair of floats before they can
+// round (double arithmetic is slow on this part).
 template <bool kVec>
 __global__ void __launch_bounds__(kGeneralThreads) seg_reduce_general_kernel(const ReduceParams p,
                                                              unsigned long long seg_elems) {
@@ -69,7 +70,7 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_reduce_general_kernel(con
 
   for (unsigned long long seg = first; seg < p.num_segments; seg += warps) {
     const uint8_t* src = p.in + seg * seg_elems * 2ull;
-    double total = 0.0;
+    float tot_h = 0.f, tot_l = 0.f;
     Acc ah = zero, al = zero;
     int pending = 0;
     for (unsigned long long v0 = 0; v0 < vecs; v0 += 32) {
@@ -92,25 +93,30 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_reduce_general_kernel(con
       ah = mma_ones(h, ah);
       al = mma_ones(l, al);
       if (++pending == kFlushEvery) {
-        total += ((double)ah.d0 + (double)ah.d2) + ((double)al.d0 + (double)al.d2);
+        pair_add(tot_h, tot_l, ah.d0, al.d0);
+        pair_add(tot_h, tot_l, ah.d2, al.d2);
         ah = al = zero;
         pending = 0;
       }
     }
-    total += ((double)ah.d0 + (double)ah.d2) + ((double)al.d0 + (double)al.d2);
+    pair_add(tot_h, tot_l, ah.d0, al.d0);
+    pair_add(tot_h, tot_l, ah.d2, al.d2);
     // every lane of a group holds the sums of rows g and g+8: add up the 8 groups
 #pragma unroll
-    for (int off = 4; off <= 16; off <<= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+    for (int off = 4; off <= 16; off <<= 1) {
+      const float oh = __shfl_xor_sync(0xffffffffu, tot_h, off), ol = __shfl_xor_sync(0xffffffffu, tot_l, off);
+      pair_add(tot_h, tot_l, oh, ol);
+    }
     if (lane == 0) {
-      store_seg(p.out, p.out_is_f32 != 0, seg, (float)total);
-      if (p.out_f64 != nullptr) p.out_f64[seg] = total;
+      store_seg(p.out, p.out_is_f32 != 0, seg, tot_h + tot_l);
+      if (p.out_f64 != nullptr) p.out_f64[seg] = (double)tot_h + (double)tot_l;
     }
   }
 }
 
 // One warp per segment, 256 elements per step as 16 rows of 16 consecutive
 // elements: A.U scans every row, an all-ones MMA gives the row totals, shuffles
-// turn them into row carries, and the running carry of the segment (a double)
+// turn them into row carries, and the running carry of the segment (two floats)
 // joins them in the accumulator operand.  Elements past the end of the segment
 // are read as zeros and not stored.
 template <bool OUT32, bool kVec>
@@ -130,7 +136,7 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
 
   for (unsigned long long seg = first; seg < num_segments; seg += warps) {
     const unsigned long long seg_base = seg * seg_elems;
-    double carry = 0.0;
+    float xh = 0.f, xl = 0.f;  // the segment so far: an exact multiple of 2^-13 plus a small rest
     for (unsigned long long e0 = 0; e0 < seg_elems; e0 += 256) {
       const uint8_t* src = p.in + (seg_base + e0) * 2ull;
       const long long left = (long long)(seg_elems - e0);  // elements of the segment from this step on
@@ -155,9 +161,6 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
       const Acc th = mma_ones(ah, zero), tl = mma_ones(al, zero);
       float ch_lo, cl_lo, ch_hi, cl_hi, step_h, step_l;
       row_carries<16>(th, tl, g, ch_lo, cl_lo, ch_hi, cl_hi, step_h, step_l);
-      // the segment so far, as an exact multiple of 2^-13 plus a small rest
-      const double carry_hi = rint(carry * 8192.0) * (1.0 / 8192.0);
-      const float xh = (float)carry_hi, xl = (float)(carry - (double)xh);
       // a large xh is held back and added last (see scan_step_independent)
       const bool fold = fabsf(xh) < 1024.f;
       const float xf = fold ? xh : 0.f, big = fold ? 0.f : xh;
@@ -180,7 +183,8 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
         store_masked<OUT32>(p.out, out_lo, n_lo, r0, r1, r2, r3);
         store_masked<OUT32>(p.out, out_hi, n_hi, q0, q1, q2, q3);
       }
-      carry += (double)step_h + (double)step_l;
+      pair_add(xh, xl, step_h, step_l);
+      pair_renorm(xh, xl);
     }
   }
 }
@@ -202,7 +206,8 @@ struct RowsParams {
   void* out;
   double* out_f64;                 // reduction only, may be null
   unsigned long long num_segments;
-  unsigned int rows_per_segment;   // m = segment_size / 16
+  unsigned int rows_per_segment;   // m = segment_size / 16 (scan)
+  unsigned int segment_bytes;      // reduction: any multiple of 16 bytes
   unsigned int segs_per_chunk;     // whole segments a warp takes at a time
   int out_is_f32;
   int exclusive;                   // scan only
@@ -218,7 +223,7 @@ __device__ __forceinline__ void fetch_row_prefix(int a, float eh_lo, float el_lo
   l = a < 8 ? l0 : l1;
 }
 
-template <bool kScan, bool OUT32>
+template <bool OUT32>
 __global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsParams p) {
   pdl_prologue();
   using Geom = ScanGeom<4>;  // linear rows: row r of a step = its elements [16r, 16r + 16)
@@ -227,6 +232,7 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsPar
   const unsigned long long first =
       (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
   const unsigned int m = p.rows_per_segment;
+  const unsigned int step_q = 16u % m, step_s = 16u / m;
   const unsigned long long chunks = (p.num_segments + p.segs_per_chunk - 1) / p.segs_per_chunk;
   const ScanOperands ops = make_scan_operands(lane, p.exclusive != 0);
   const Acc zero{0.f, 0.f, 0.f, 0.f};
@@ -241,7 +247,7 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsPar
     // this lane's two rows of the current step: position inside their segment, segment in the chunk
     unsigned int q_lo = (unsigned)g % m, s_lo = (unsigned)g / m;
     unsigned int q_hi = (unsigned)(g + 8) % m, s_hi = (unsigned)(g + 8) / m;
-    double open_run = 0.0;  // what the segment that is open at the start of the step has so far
+    float open_h = 0.f, open_l = 0.f;  // what the segment that is open at the start of the step has so far
     // the loads of the next three steps are in flight while one step is worked on
     constexpr int kAhead = 3;
     uint2 nlo[kAhead], nhi[kAhead];
@@ -276,30 +282,21 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsPar
       const float xh_lo = here_lo ? eh_lo - bh : eh_lo, xl_lo = here_lo ? el_lo - bl : el_lo;
       fetch_row_prefix(here_hi ? g + 8 - (int)q_hi : 0, eh_lo, el_lo, eh_hi, el_hi, bh, bl);
       const float xh_hi = here_hi ? eh_hi - bh : eh_hi, xl_hi = here_hi ? el_hi - bl : el_hi;
-      // ... plus what the segment brought along, if it began in an earlier step
-      const double carry_lo = (here_lo ? 0.0 : open_run) + (double)xh_lo + (double)xl_lo;
-      const double carry_hi = (here_hi ? 0.0 : open_run) + (double)xh_hi + (double)xl_hi;
-      const double incl_lo = carry_lo + (double)th.d0 + (double)tl.d0;
-      const double incl_hi = carry_hi + (double)th.d2 + (double)tl.d2;
+      // ... plus what the segment brought along, if it began in an earlier step.  Sums are kept
+      // as two floats, of the hi parts and of the lo parts: a segment is at most 2048 elements,
+      // so both are exact while the sum stays below 2^11 and rounded like any float sum above.
+      float ch_lo = (here_lo ? 0.f : open_h) + xh_lo, cl_lo = (here_lo ? 0.f : open_l) + xl_lo;
+      float ch_hi = (here_hi ? 0.f : open_h) + xh_hi, cl_hi = (here_hi ? 0.f : open_l) + xl_hi;
+      const float ih_hi = ch_hi + th.d2, il_hi = cl_hi + tl.d2;  // through the step's last row, in lane 28
 
-      if constexpr (!kScan) {
-        if (t == 0) {
-          if (ok_lo && q_lo == m - 1) {
-            store_seg(p.out, p.out_is_f32 != 0, seg0 + s_lo, (float)incl_lo);
-            if (p.out_f64 != nullptr) p.out_f64[seg0 + s_lo] = incl_lo;
-          }
-          if (ok_hi && q_hi == m - 1) {
-            store_seg(p.out, p.out_is_f32 != 0, seg0 + s_hi, (float)incl_hi);
-            if (p.out_f64 != nullptr) p.out_f64[seg0 + s_hi] = incl_hi;
-          }
-        }
-      } else {
+      {
         // the carry of each row as an exact multiple of 2^-13 plus a small rest; a large one is
         // held back and added last (see scan_step_independent)
-        const double c13_lo = rint(carry_lo * 8192.0) * (1.0 / 8192.0);
-        const double c13_hi = rint(carry_hi * 8192.0) * (1.0 / 8192.0);
-        float ch_lo = (float)c13_lo, ch_hi = (float)c13_hi;
-        const float cl_lo = (float)(carry_lo - (double)ch_lo), cl_hi = (float)(carry_hi - (double)ch_hi);
+        const float m_lo = grid13(cl_lo), m_hi = grid13(cl_hi);
+        ch_lo += m_lo;
+        cl_lo -= m_lo;
+        ch_hi += m_hi;
+        cl_hi -= m_hi;
         float big_lo = 0.f, big_hi = 0.f;
         if (fabsf(ch_lo) >= 1024.f) { big_lo = ch_lo; ch_lo = 0.f; }
         if (fabsf(ch_hi) >= 1024.f) { big_hi = ch_hi; ch_hi = 0.f; }
@@ -317,14 +314,106 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsPar
                         (ha.d3 + la.d3) + big_hi, (hb.d2 + lb.d2) + big_hi, (hb.d3 + lb.d3) + big_hi);
       }
       // the segment of the step's last row stays open unless that row ends it
-      const double through15 = __shfl_sync(0xffffffffu, incl_hi, 28);
-      const unsigned int q15    = __shfl_sync(0xffffffffu, q_hi, 28);
-      open_run = q15 == m - 1 ? 0.0 : through15;
-      q_lo += 16;
-      while (q_lo >= m) { q_lo -= m; ++s_lo; }
-      q_hi += 16;
-      while (q_hi >= m) { q_hi -= m; ++s_hi; }
+      const float t15_h = __shfl_sync(0xffffffffu, ih_hi, 28), t15_l = __shfl_sync(0xffffffffu, il_hi, 28);
+      const unsigned int q15 = __shfl_sync(0xffffffffu, q_hi, 28);
+      open_h = q15 == m - 1 ? 0.f : t15_h;
+      open_l = q15 == m - 1 ? 0.f : t15_l;
+      q_lo += step_q;  // 16 rows on: 16 / m segments and 16 % m rows
+      s_lo += step_s;
+      if (q_lo >= m) { q_lo -= m; ++s_lo; }
+      q_hi += step_q;
+      s_hi += step_s;
+      if (q_hi >= m) { q_hi -= m; ++s_hi; }
     }
+  }
+}
+
+// Reduction for the same segment sizes (and any other multiple of 8 elements up to 2048),
+// without the prefixes the scan needs: a warp takes 16
+// segments as the 16 rows of an MMA.  The order of the elements inside a row does not matter
+// for a sum, so a lane loads 16 consecutive bytes of "its" two segments per step (four lanes
+// cover 64 bytes of a segment, the warp whole 32-byte sectors of one contiguous range) and the
+// four registers feed two all-ones MMAs: the row sums come out complete, no shuffles.
+__global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsParams p) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const unsigned long long warps = (unsigned long long)gridDim.x * (kGeneralThreads / 32);
+  const unsigned long long first =
+      (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
+  const unsigned int seg_bytes    = p.segment_bytes;
+  const unsigned long long groups = (p.num_segments + 15) / 16;
+  const Acc zero{0.f, 0.f, 0.f, 0.f};
+  const bool f32 = p.out_is_f32 != 0;
+
+  // One round = 128 bytes of each of a group's segments: four loads per lane.  The loads of the
+  // next round (of this group or of the warp's next group) are issued before the current round
+  // is worked on.
+  auto load_round = [&](unsigned long long grp, unsigned int b, uint4 (&x)[2], uint4 (&y)[2]) {
+    const unsigned long long seg_lo = grp * 16 + g;
+    const bool ok_lo = seg_lo < p.num_segments, ok_hi = seg_lo + 8 < p.num_segments;
+    const uint8_t* src_lo = p.in + seg_lo * seg_bytes + 16u * t + b;
+    const uint8_t* src_hi = src_lo + 8ull * seg_bytes;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const bool in = b + 64u * k + 16u * t < seg_bytes;
+      x[k] = ok_lo && in ? ldg128(src_lo + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
+      y[k] = ok_hi && in ? ldg128(src_hi + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  unsigned long long grp = first;
+  unsigned int b = 0;
+  if (grp >= groups) return;
+  uint4 x[2], y[2];
+  load_round(grp, b, x, y);
+  Acc ah = zero, al = zero;
+  for (;;) {
+    unsigned long long ngrp = grp;
+    unsigned int nb = b + 128u;
+    if (nb >= seg_bytes) {
+      nb   = 0u;
+      ngrp = grp + warps;
+    }
+    const bool more = ngrp < groups;
+    uint4 nx[2], ny[2];
+    if (more) load_round(ngrp, nb, nx, ny);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      uint4 xh, xl, yh, yl;
+      split_hi_lo(x[k].x, xh.x, xl.x);
+      split_hi_lo(x[k].y, xh.y, xl.y);
+      split_hi_lo(x[k].z, xh.z, xl.z);
+      split_hi_lo(x[k].w, xh.w, xl.w);
+      split_hi_lo(y[k].x, yh.x, yl.x);
+      split_hi_lo(y[k].y, yh.y, yl.y);
+      split_hi_lo(y[k].z, yh.z, yl.z);
+      split_hi_lo(y[k].w, yh.w, yl.w);
+      ah = mma16816(xh.x, yh.x, xh.y, yh.y, kOnesH2, kOnesH2, ah);  // rows g / g + 8
+      ah = mma16816(xh.z, yh.z, xh.w, yh.w, kOnesH2, kOnesH2, ah);
+      al = mma16816(xl.x, yl.x, xl.y, yl.y, kOnesH2, kOnesH2, al);
+      al = mma16816(xl.z, yl.z, xl.w, yl.w, kOnesH2, kOnesH2, al);
+    }
+    if (nb == 0u) {  // the group's last round: every column of the accumulators holds the row sums
+      const unsigned long long seg_lo = grp * 16 + g, seg_hi = seg_lo + 8;
+      if (t == 0) {
+        if (seg_lo < p.num_segments) {
+          store_seg(p.out, f32, seg_lo, ah.d0 + al.d0);
+          if (p.out_f64 != nullptr) p.out_f64[seg_lo] = (double)ah.d0 + (double)al.d0;
+        }
+        if (seg_hi < p.num_segments) {
+          store_seg(p.out, f32, seg_hi, ah.d2 + al.d2);
+          if (p.out_f64 != nullptr) p.out_f64[seg_hi] = (double)ah.d2 + (double)al.d2;
+        }
+      }
+      ah = al = zero;
+    }
+    if (!more) break;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      x[k] = nx[k];
+      y[k] = ny[k];
+    }
+    grp = ngrp;
+    b   = nb;
   }
 }
 

@@ -330,28 +330,18 @@ __global__ void __launch_bounds__(kThreads, 1) shard_scan_kernel(const ShardPara
         wl = cl;
       }
       const float2 pr = part[i & 1][w];
-      float e;
-      two_sum(ch, pr.x, ch, e);
-      cl += pr.y + e;
+      pair_add(ch, cl, pr.x, pr.y);
     }
-    {  // multiples of 2^-13 that the lo parts have added up to move over to the coarse part
-      const float m = grid13(cl);
-      float e;
-      two_sum(ch, m, rh, e);
-      rl = (cl - m) + e;
-    }
+    rh = ch;
+    rl = cl;
+    pair_renorm(rh, rl);  // multiples of 2^-13 that the lo parts have added up to move over
     if (!active) continue;
 
     // everything before this slice as two floats: xh a multiple of 2^-13, xl the
     // rest.  Below 2^10, xh rides through the accumulators with the row carries
     // (every sum stays exact); above, it is added to each output last.
-    float xh, xl;
-    {
-      const float m = grid13(wl);
-      float e;
-      two_sum(wh, m, xh, e);
-      xl = (wl - m) + e;
-    }
+    float xh = wh, xl = wl;
+    pair_renorm(xh, xl);
     const bool fold = fabsf(xh) < 1024.f;
     const float xf = fold ? xh : 0.f, big = fold ? 0.f : xh;
     RowCarry rc{ch_lo + xf, cl_lo + xl, ch_hi + xf, cl_hi + xl};

@@ -349,12 +349,8 @@ __global__ void __launch_bounds__(512, 1)
               cb = nb;
             }
           }
-          float e1, e2;
-          two_sum(rh, th, rh, e1);
-          rl += tl + e1;
-          const float m = grid13(rl);
-          two_sum(rh, m, rh, e2);
-          rl = (rl - m) + e2;
+          pair_add(rh, rl, th, tl);
+          pair_renorm(rh, rl);
         }
       }
 

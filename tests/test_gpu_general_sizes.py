@@ -10,7 +10,7 @@ import oracle
 pytestmark = pytest.mark.gpu
 
 SIZES = [48, 80, 240, 272, 768, 1008, 4112, 16000, 3 * 16384, 100016,   # multiples of 16
-         1, 2, 3, 8, 12, 20, 100, 255, 257, 1000, 1001, 4099, 65537]      # everything else
+         1, 2, 3, 8, 12, 20, 24, 100, 255, 257, 1000, 1001, 2040, 4099, 65537]  # everything else
 
 
 def bits(t):
