@@ -276,13 +276,24 @@ cudaError_t launch_tcgen05_reduce(const ReduceParams& p, const CUtensorMap& map,
 bool make_output_tensor_map(CUtensorMap* map, void* d_out, size_t num_elems, bool out32) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc || num_elems % kSwizzleRowElems != 0) return false;
-  const cuuint64_t dims[2]    = {kSwizzleRowElems, num_elems / kSwizzleRowElems};
-  const cuuint64_t strides[1] = {cuuint64_t(kSwizzleRowElems) * (out32 ? 4 : 2)};
-  const cuuint32_t box[2]     = {out32 ? 32u : 64u, 32u};
-  const cuuint32_t estr[2]    = {1, 1};
-  if (dims[1] >= (cuuint64_t(1) << 31)) return false;
-  return enc(map, out32 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d_out,
-             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const cuuint64_t rows = num_elems / kSwizzleRowElems;
+  if (rows >= (cuuint64_t(1) << 31)) return false;
+  const cuuint32_t estr[3] = {1, 1, 1};
+  if (out32) {
+    // A row of 64 floats is two swizzle spans of 128 bytes: the view {32 floats, 2 halves, rows}
+    // lets one box hold whole rows (32 rows, 8 KiB contiguous in global memory).
+    const cuuint64_t dims[3]    = {32, 2, rows};
+    const cuuint64_t strides[2] = {128, 256};
+    const cuuint32_t box[3]     = {32, 2, 32};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, d_out, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  const cuuint64_t dims[2]    = {kSwizzleRowElems, rows};
+  const cuuint64_t strides[1] = {cuuint64_t(kSwizzleRowElems) * 2};
+  const cuuint32_t box[2]     = {64u, 32u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d_out, dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

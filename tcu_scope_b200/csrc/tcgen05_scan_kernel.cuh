@@ -100,6 +100,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, int c0, in
                : "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, int c0, int c1, int c2, uint32_t src_smem) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(src_smem)
+               : "memory");
+}
+
 // Registers are per SM sub-partition (16 K): 14 warps put four on one, so a thread may use 128
 // at most.  A bound of 512 threads makes the compiler keep to exactly that.
 template <int LOG2S, bool OUT32>
@@ -138,7 +144,7 @@ __global__ void __launch_bounds__(512, 1)
   // groups whose tiles alternate (tile i of the unit belongs to group i % 2): the two sets of
   // epilogue warps, which take alternate tiles, then own one group each.
   const unsigned long long num_units =
-      G == 1 ? (num_rows + kUmmaRows - 1) / kUmmaRows
+      G == 1 ? (num_rows + kPer * kUmmaRows - 1) / (kPer * kUmmaRows)
              : (num_rows + 2ull * G * kUmmaRows - 1) / (2ull * G * kUmmaRows);
   auto unit_of = [&](uint32_t i) -> unsigned long long {
     return blockIdx.x + (unsigned long long)(i / kPer) * gridDim.x;
@@ -146,7 +152,7 @@ __global__ void __launch_bounds__(512, 1)
   // First of the 32 rows that quarter q of this CTA's i-th tile holds.
   auto quarter_row = [&](uint32_t i, int q) -> unsigned long long {
     if constexpr (G == 1) {
-      return unit_of(i) * kUmmaRows + 32ull * q;
+      return (unit_of(i) * kPer + i % kPer) * kUmmaRows + 32ull * q;
     } else {
       const uint32_t r = i % kPer;
       const unsigned long long group = 2ull * unit_of(i) + (r & 1u);
@@ -203,10 +209,14 @@ __global__ void __launch_bounds__(512, 1)
         const uint32_t dst = raw_u32 + s * kUmmaTileBytes, bar = raw_full0 + 8 * s;
         if constexpr (G == 1) {
           const unsigned long long row = quarter_row(i, 0);
-          const unsigned long long rem = (num_rows - row) * 128ull;
-          const uint32_t bytes = rem < (unsigned long long)kUmmaTileBytes ? (uint32_t)rem : kUmmaTileBytes;
-          mbar_arrive_expect_tx(bar, bytes);
-          tma_load_1d(dst, p.in + row * 128ull, bytes, bar);
+          if (row >= num_rows) {
+            mbar_arrive(bar);
+          } else {
+            const unsigned long long rem = (num_rows - row) * 128ull;
+            const uint32_t bytes = rem < (unsigned long long)kUmmaTileBytes ? (uint32_t)rem : kUmmaTileBytes;
+            mbar_arrive_expect_tx(bar, bytes);
+            tma_load_1d(dst, p.in + row * 128ull, bytes, bar);
+          }
         } else {
           // whole segments only: a quarter's 32 rows are all inside the array or all outside
           uint32_t pieces = 0;
@@ -357,10 +367,12 @@ __global__ void __launch_bounds__(512, 1)
       const float2 cb2 = make_float2(cb, cb), cs2 = make_float2(cs, cs);
       const bool any_big = S > 2048 && __any_sync(0xffffffffu, big != 0.f);
       // This thread's outputs go to the warp's staging buffers as box rows of 128 bytes with the
-      // 128-byte swizzle the tensor map expects (16-byte chunk index XOR row mod 8: the lanes'
-      // stores spread over all banks) and leave through bulk tensor stores.  Two buffers per
-      // warp: 16-bit outputs fill one per tile (a row is 128 bytes), fp32 outputs one per half
-      // row, so the copy of one buffer overlaps the filling of the other.
+      // 128-byte swizzle the tensor map expects (16-byte chunk index XOR box row mod 8) and leave
+      // through bulk tensor stores.  16-bit outputs: a row is one box row, the warp's two
+      // buffers take alternate tiles, so the copy of one overlaps the filling of the other.
+      // fp32 outputs: a row is two box rows of one 8 KiB box (view {32 floats, 2 halves, rows}),
+      // stored whole -- 8 KiB contiguous in global memory per copy; two copies of alternate
+      // 128-byte pieces measured 0.86 of the copy bandwidth where the mma.sync kernels reach 0.97.
       const unsigned long long row0 = quarter_row(i, quarter);  // first row of this warp
       uint8_t* const bufs = stage + (set * 4 + quarter) * 2 * kUscanStageBytes;
 #pragma unroll
@@ -375,12 +387,13 @@ __global__ void __launch_bounds__(512, 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty0 + 8 * a);  // the accumulators are in registers now
         }
-        uint8_t* const buf = bufs + (OUT32 ? half : (int)((i >> 1) & 1u)) * kUscanStageBytes;
-        if (OUT32 || half == 0) {
-          if (lane == 0) bulk_wait_group_read<1>();  // the store that last read this buffer is done
+        uint8_t* const buf = bufs + (OUT32 ? 0 : (int)((i >> 1) & 1u)) * kUscanStageBytes;
+        if (half == 0) {
+          if (lane == 0) bulk_wait_group_read<OUT32 ? 0 : 1>();  // the store that last read this buffer is done
           __syncwarp();
         }
-        uint8_t* const my_row = buf + lane * 128;
+        uint8_t* const my_row = buf + (OUT32 ? lane * 256 + half * 128 : lane * 128);
+        const int key = OUT32 ? (2 * lane + half) & 7 : lane & 7;  // box row mod 8
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           float o[16];
@@ -401,24 +414,29 @@ __global__ void __launch_bounds__(512, 1)
 #pragma unroll
             for (int e = 0; e < 16; e += 4) {
               const int j = cc * 4 + e / 4;
-              *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 7)) << 4)) =
+              *reinterpret_cast<float4*>(my_row + ((j ^ key) << 4)) =
                   make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
             }
           } else {  // the whole row is one box row of 64 halves
 #pragma unroll
             for (int e = 0; e < 16; e += 8) {
               const int j = 2 * (2 * half + cc) + e / 8;
-              *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) =
+              *reinterpret_cast<uint4*>(my_row + ((j ^ key) << 4)) =
                   make_uint4(pack2_rn(o[e], o[e + 1]), pack2_rn(o[e + 2], o[e + 3]),
                              pack2_rn(o[e + 4], o[e + 5]), pack2_rn(o[e + 6], o[e + 7]));
             }
           }
         }
-        if (OUT32 || half == 1) {
+        if (half == 1) {
           fence_proxy_async_smem();  // generic writes of the buffer, before the bulk store reads it
           __syncwarp();
           if (lane == 0) {
-            if (row0 < num_rows) tma_store_2d(&omap, OUT32 ? 32 * half : 0, (int)row0, smem_u32(buf));
+            if (row0 < num_rows) {
+              if constexpr (OUT32)
+                tma_store_3d(&omap, 0, 0, (int)row0, smem_u32(buf));
+              else
+                tma_store_2d(&omap, 0, (int)row0, smem_u32(buf));
+            }
             bulk_commit_group();
           }
         }
