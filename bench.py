@@ -779,7 +779,8 @@ def ablation_leg(torch, tcu, args):
         red[str(s)] = round(n / ms / 1e6, 1)
     out["reduce"]["tcgen05"] = red
     sc = {}
-    for s, dt in [(16, torch.float16), (256, torch.float16), (2048, torch.float16), (4096, torch.float32)]:
+    for s, dt in [(16, torch.float16), (256, torch.float16), (2048, torch.float16), (16384, torch.float16),
+                  (4096, torch.float32)]:
         o = torch.empty(n, dtype=dt, device="cuda")
         for algo in ("mma", "tcgen05"):
             def call():
@@ -793,7 +794,7 @@ def ablation_leg(torch, tcu, args):
                    "does not split inputs into exact parts (plain fp32 rounding); tcgen05 = "
                    "tcgen05.mma with the accumulator in tensor memory: reductions up to 2048 elements per "
                    "segment with plain fp32 accumulation, scans with the exact parts of the mma.sync path "
-                   "(the default for 16-bit outputs of 16- and 256...2048-element segments)")
+                   "(the default for 16-bit outputs of 16- and 256...16384-element segments)")
     return out
 
 
