@@ -479,10 +479,13 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   }
   // TCU_ALGO_AUTO takes the tcgen05 kernel where it measured faster than the mma.sync one:
   // 16-bit outputs of 16- and 256 ... 16384-element segments (0.95 ... 0.97 of the copy bandwidth
-  // at 2^28 elements against 0.92 / 0.93 ... 0.76), from 2^25 elements on (its set-up costs
-  // 3-4 us more).
+  // at 2^28 elements against 0.92 / 0.93 ... 0.76).  Its set-up costs 3-4 us more, so it takes
+  // over from 2^26 elements on for segments of 2048 and more (47.7 against 51.2 us at 2048,
+  // 54.1 against 57.5 us at 16384) and from 2^27 on for the shorter ones (a tie at 2^26,
+  // 87.7 against 90.8 us at 2^27 and 16-element segments).
+  const size_t umma_from = sc >= 11 ? size_t(1) << 26 : size_t(1) << 27;
   const bool umma_auto = algo == TCU_ALGO_AUTO && !f32 && !exclusive && n % kSwizzleRowElems == 0 &&
-                         n >= (size_t(1) << 25) && (sc == 4 || (sc >= 8 && sc <= 14));
+                         n >= umma_from && (sc == 4 || (sc >= 8 && sc <= 14));
   if (algo == TCU_ALGO_TCGEN05 || umma_auto) {
     CUtensorMap omap;
     std::memset(&omap, 0, sizeof(omap));
