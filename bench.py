@@ -74,13 +74,13 @@ def parse_args():
                          "segment: use it with --profile reduce or --profile scan")
     ap.add_argument("--log2-elems", type=int, default=LOG2_ELEMS,
                     help="elements per GPU (default 28, the reference sweep's size)")
-    ap.add_argument("--profile", default=None, choices=["reduce", "scan", "scan16", "full", "shard", "general"],
+    ap.add_argument("--profile", default=None, choices=["reduce", "scan", "scan16", "scan32", "full", "shard", "general"],
                     help="run ONE untimed pass of the named kernels at --log2-elems and exit "
                          "(the small case an ncu capture wraps)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the other configurations, the e2e leg and the CPU baseline")
     args = ap.parse_args()
-    if args.algo == "tcgen05" and args.profile not in ("reduce", "scan", "scan16"):
+    if args.algo == "tcgen05" and args.profile not in ("reduce", "scan", "scan16", "scan32"):
         ap.error("--algo tcgen05 does not cover every size of the sweep: use it with --profile reduce "
                  "or --profile scan (the timed run reports it under ablation_tensor_core_vs_shuffle)")
     return args
@@ -872,6 +872,9 @@ def profile_pass(torch, tcu, args, n, json_fd):
     elif args.profile == "scan16":  # the classes with 16-bit outputs that stay under 0.90
         for s in (2048, 4096, 16384):
             tcu.segmented_scan(x, s, out_dtype=torch.float16, algo=args.algo)
+    elif args.profile == "scan32":  # the fp32-output classes under 0.90, and their neighbours
+        for s in (16, 32, 64, 128):
+            tcu.segmented_scan(x, s, out_dtype=torch.float32, algo=args.algo)
     elif args.profile == "general":  # a segment size that is a multiple of 16 but no power of two
         x = x[:n // 48 * 48]
         tcu.segmented_reduce(x, 48)

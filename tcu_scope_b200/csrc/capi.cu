@@ -204,10 +204,10 @@ cudaError_t launch_reduce(const ReduceParams& p, int grid, cudaStream_t st) {
 template <int SC, bool OUT32>
 cudaError_t launch_scan(const ScanParams& p, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
-  cudaError_t e = ensure_smem(seg_scan_kernel<SC, OUT32>, configured, scan_dyn_smem_bytes(SC));
+  cudaError_t e = ensure_smem(seg_scan_kernel<SC, OUT32>, configured, scan_dyn_smem_bytes(SC, OUT32));
   if (e != cudaSuccess) return e;
-  return launch_pdl(seg_scan_kernel<SC, OUT32>, p, grid * scan_ctas_per_sm(SC),
-                    SliceShape<scan_warps(SC, OUT32)>::kThreads, scan_dyn_smem_bytes(SC), st);
+  return launch_pdl(seg_scan_kernel<SC, OUT32>, p, grid * scan_ctas_per_sm(SC, OUT32),
+                    SliceShape<scan_warps(SC, OUT32)>::kThreads, scan_dyn_smem_bytes(SC, OUT32), st);
 }
 
 // cuTensorMapEncodeTiled, looked up once through the runtime (no link against libcuda).

@@ -305,16 +305,25 @@ __device__ __forceinline__ void scan_step_independent(int j, const uint32_t (&ah
 __host__ __device__ constexpr int scan_warps(int sc, bool out32) {
   return !out32 && (sc == 6 || (sc >= 8 && sc <= 10)) ? 16 : 8;
 }
-constexpr int kScan2CtaMaxClass  = 4;  // largest class that runs two CTAs per SM
-constexpr int kScan2CtaStages    = 3;
-constexpr int kScanBulkMaxClass  = 6;  // largest class whose fp16 outputs leave through shared memory
-constexpr int kScanBulkStages    = 5;  // those classes hold a stage one tile longer
-__host__ __device__ constexpr int scan_ctas_per_sm(int sc) { return sc <= kScan2CtaMaxClass ? 2 : 1; }
-__host__ __device__ constexpr int scan_stages(int sc) {
-  return scan_ctas_per_sm(sc) == 2 ? kScan2CtaStages
-                                   : (sc <= kScanBulkMaxClass ? kScanBulkStages : kStages);
+constexpr int kScanBulkMaxClass = 6;  // largest class whose fp16 outputs leave through shared memory
+// Two CTAs per SM (3-stage rings) only for 16-bit outputs of 16-element segments; everything else
+// reads and splits the slice once into registers, one CTA per SM.  Ring depth, measured at 2^28
+// elements: the classes whose fp16 outputs leave through the ring stage hold a stage one tile
+// longer (5 stages); fp32 outputs of 16 ... 64-element segments run faster on a SHALLOW ring of 2
+// stages, and the 16-element ones on one CTA per SM at that (0.91 / 0.96 / 0.96 of the copy
+// bandwidth against 0.87 / 0.93 / 0.89 with 2 x 3 and 5 stages: reads that run far ahead get in
+// the way of twice as many bytes of writes); the others measured best with 4 (2 stages: fp32
+// outputs of 4096 and 8192 elements -2 %, fp16 outputs from 256 elements on between -3 and +5 %
+// from box to box).
+__host__ __device__ constexpr int scan_ctas_per_sm(int sc, bool out32) { return sc == 4 && !out32 ? 2 : 1; }
+__host__ __device__ constexpr int scan_stages(int sc, bool out32) {
+  if (scan_ctas_per_sm(sc, out32) == 2) return 3;
+  if (out32) return sc <= 6 ? 2 : kStages;
+  return sc <= kScanBulkMaxClass ? 5 : kStages;
 }
-__host__ __device__ constexpr int scan_dyn_smem_bytes(int sc) { return scan_stages(sc) * kTileBytes + 128; }
+__host__ __device__ constexpr int scan_dyn_smem_bytes(int sc, bool out32) {
+  return scan_stages(sc, out32) * kTileBytes + 128;
+}
 
 template <int kWarps>
 __device__ __forceinline__ void consumer_sync_n() {
@@ -322,15 +331,15 @@ __device__ __forceinline__ void consumer_sync_n() {
 }
 
 template <int SC, bool OUT32, int W = scan_warps(SC, OUT32)>
-__global__ void __launch_bounds__(SliceShape<W>::kThreads, scan_ctas_per_sm(SC))
+__global__ void __launch_bounds__(SliceShape<W>::kThreads, scan_ctas_per_sm(SC, OUT32))
     seg_scan_kernel(const ScanParams p) {
   static_assert(SC >= 4 && SC <= 14, "the look-back class has its own kernel");
   using Shape = SliceShape<W>;
   using Geom  = ScanGeom<SC, W>;
-  constexpr int kStages = scan_stages(SC);  // shadows the library-wide ring depth
+  constexpr int kStages = scan_stages(SC, OUT32);  // shadows the library-wide ring depth
   constexpr int kSteps  = Shape::kSteps;
   constexpr int LR      = Shape::kRowElemsLog2;
-  constexpr bool kScanCache = scan_ctas_per_sm(SC) == 1;  // slice kept in registers between passes
+  constexpr bool kScanCache = scan_ctas_per_sm(SC, OUT32) == 1;  // slice kept in registers between passes
   // segments longer than a row: rows per segment inside the slice, warps per segment beyond
   constexpr bool kRows      = SC > LR;
   constexpr int kRowsPerSeg = SC >= LR + 4 ? 16 : (kRows ? 1 << (SC - LR) : 1);
