@@ -34,7 +34,7 @@
 
 namespace TCU_NS {
 
-constexpr int kUscanRawStages   = 4;                   // 16 KiB tiles as the TMA copies deliver them
+constexpr int kUscanRawStages   = 5;                   // 16 KiB tiles as the TMA copies deliver them (at most)
 constexpr int kUscanSplitStages = 2;                   // (hi, lo) tile pairs, 32 KiB each
 constexpr int kUscanAccStages   = 2;                   // accumulator pairs in tensor memory
 constexpr int kUscanN           = 64;                  // columns of U = outputs per row
@@ -122,7 +122,12 @@ __global__ void __launch_bounds__(512, 1)
   constexpr int kPer         = G == 1 ? 1 : 2 * G;  // tiles of one work unit (a tile, or two groups)
   constexpr int kRowsPerSeg  = S <= 64 ? 1 : (G > 1 ? 32 : S / 64);  // rows of a segment in a tile
   constexpr int kLanesPerSeg = kRowsPerSeg;
-  constexpr int NR = kUscanRawStages, NH = kUscanSplitStages, NA = kUscanAccStages;
+  // Depth of the input ring, measured at 2^28 elements (2 / 3 / 4 / 5 stages): fp32 outputs 0.90 /
+  // 0.96 / 0.89 / -- of the copy bandwidth at every segment size (reads that run far ahead get in
+  // the way of twice as many bytes of writes); 16-bit outputs 0.81 / 0.91 / 0.98 / 0.99 from 256
+  // elements on, and 0.81 / 0.91 / 0.98 / 0.90 for 16-element segments.
+  constexpr int NR = OUT32 ? 3 : (LOG2S == 4 ? 4 : kUscanRawStages);
+  constexpr int NH = kUscanSplitStages, NA = kUscanAccStages;
   extern __shared__ uint8_t dyn_smem[];
   // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty
   __shared__ __align__(8) uint64_t bars[2 * NR + 2 * NH + 2 * NA];

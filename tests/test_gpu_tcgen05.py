@@ -95,15 +95,20 @@ def test_tcgen05_scan_rejects_what_it_does_not_cover():
         tcu.segmented_scan(x[:4096 - 16], 16, algo="tcgen05")  # element count not a multiple of 64
 
 
-@pytest.mark.parametrize("s", [16, 2048, 16384])
-def test_auto_runs_the_tcgen05_scan_on_large_16bit_outputs(s):
+@pytest.mark.parametrize("s,out_dtype", [(16, torch.float16), (2048, torch.float16), (16384, torch.float16),
+                                         (16, torch.float32)])
+def test_auto_runs_the_tcgen05_scan_on_large_arrays(s, out_dtype):
     """TCU_ALGO_AUTO switches to the tensor-memory scan from 2^26 / 2^27 elements on: the default
     path of a large scan is checked against the oracle like the explicit one."""
     import tcu_scope_b200 as tcu
     n = 1 << 27
     x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 123, 0)
-    out = tcu.segmented_scan(x, s, out_dtype=torch.float16)
-    bad, worst = oracle.np_check_f16(bits(out), oracle.c_segmented_scan(bits(x), s), 2)
-    assert bad == 0 and worst <= 1
-    assert torch.equal(out, tcu.segmented_scan(x, s, out_dtype=torch.float16, algo="tcgen05"))
+    out = tcu.segmented_scan(x, s, out_dtype=out_dtype)
+    ref = oracle.c_segmented_scan(bits(x), s)
+    if out_dtype == torch.float32:
+        assert np.array_equal(out.cpu().numpy(), ref.astype(np.float32))
+    else:
+        bad, worst = oracle.np_check_f16(bits(out), ref, 2)
+        assert bad == 0 and worst <= 1
+    assert torch.equal(out, tcu.segmented_scan(x, s, out_dtype=out_dtype, algo="tcgen05"))
     assert tcu.device_error() == 0
