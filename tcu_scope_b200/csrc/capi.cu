@@ -369,7 +369,10 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   g_test_skip_tile = ~0ull;
 #endif
   const size_t tiles = (n + kTileElems - 1) / kTileElems;
-  int grid           = tiles < size_t(sms) ? int(tiles) : sms;
+  // work units: tiles, or, for segments of 4096 ... 16384 elements, groups of eight segments
+  const size_t units = sc >= 12 && sc <= 14 ? (num_segments + 7) / 8 : tiles;
+  int grid           = units < size_t(sms) ? int(units) : sms;
+  if (grid < 1) grid = 1;
 
   cudaError_t e = cudaSuccess;
   if (sc == kClassGeneral && segment_size % 8 == 0 && segment_size <= 2048) {

@@ -232,7 +232,6 @@ template <int SC, bool kTensor = true>
 __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReduceParams p) {
   extern __shared__ uint8_t dyn_smem[];
   __shared__ __align__(8) uint64_t bars[2 * kStages];
-  __shared__ float2 part[2][kConsumerWarps];  // slice totals of the tile in flight
   __shared__ double warp_sum[2][kConsumerWarps];  // long class: per-warp running sums of a segment
   __shared__ int s_is_last;
 
@@ -241,6 +240,14 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
   const uint32_t ring_u32 = smem_u32(ring);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kStages]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Segments of 2, 4 or 8 slices: a stage of the ring does not hold 32 KiB of consecutive input
+  // but one slice of each of eight consecutive segments, so that warp w meets the G slices of
+  // "its" segment in G consecutive stages and adds them up in registers.  No warp ever needs
+  // another warp's sum (one barrier of the consumer warps per tile measured 1.01 / 0.97 / 0.95
+  // of the copy bandwidth at 4096 / 8192 / 16384 elements, a collector warp 0.93).
+  constexpr bool kSpread = SC >= 12 && SC <= 14;
+  constexpr int G        = kSpread ? 1 << (SC - 11) : 1;
+  const unsigned long long num_units = (p.num_segments + kConsumerWarps - 1) / kConsumerWarps;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -271,7 +278,24 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
 
   if (warp == kConsumerWarps) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
+    if (lane == 0 && kSpread) {
+      uint32_t i = 0;
+      bool ok = true;
+      for (unsigned long long unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
+        const unsigned long long seg0 = unit * kConsumerWarps;
+        const unsigned long long left = p.num_segments - seg0;
+        const uint32_t segs = left < (unsigned long long)kConsumerWarps ? (uint32_t)left : kConsumerWarps;
+        for (int j = 0; j < G; ++j, ++i) {
+          const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) { ok = false; break; }
+          mbar_arrive_expect_tx(full0 + 8 * s, segs * kSliceBytes);
+          for (uint32_t w = 0; w < segs; ++w)  // slice j of segment seg0 + w
+            tma_load_1d(ring_u32 + s * kTileBytes + w * kSliceBytes,
+                        p.in + ((seg0 + w) * G + j) * (unsigned long long)kSliceBytes, kSliceBytes,
+                        full0 + 8 * s);
+        }
+      }
+    } else if (lane == 0) {
       uint32_t i = 0;
       for (unsigned long long tile = tile_begin; tile < tile_end; tile += tile_step, ++i) {
         const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
@@ -329,8 +353,34 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
       }
     };
 
+    if constexpr (kSpread) {
+      uint32_t i = 0;
+      for (unsigned long long unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
+        const unsigned long long seg = unit * kConsumerWarps + warp;
+        const bool valid = seg < p.num_segments;  // else the stage holds nothing for this warp
+        float acc_h = 0.f, acc_l = 0.f;  // compensated pair: exact hi-part sum, lo parts + round-off
+#pragma unroll 1
+        for (int j = 0; j < G; ++j, ++i) {
+          const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
+          if (!dead && !mbar_wait(full0 + 8 * s, ph)) dead = true;
+          float2 tot = make_float2(0.f, 0.f);
+          if (!dead && valid) {
+            const uint8_t* slice = ring + s * kTileBytes + warp * kSliceBytes;
+            if constexpr (kTensor)
+              tot = reduce_slice<SC>(slice, p.out, out_f32, 0, 0, lane);
+            else
+              tot = shuffle_reduce_slice<SC>(slice, p.out, out_f32, 0, 0, lane);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty0 + 8 * s);
+          pair_add(acc_h, acc_l, tot.x, tot.y);
+        }
+        if (lane == 0 && valid && !dead) store_seg(p.out, out_f32, seg, acc_h + acc_l);
+      }
+    }
+
     uint32_t i = 0;
-    for (unsigned long long tile = tile_begin; tile < tile_end; tile += tile_step, ++i) {
+    for (unsigned long long tile = kSpread ? tile_end : tile_begin; tile < tile_end; tile += tile_step, ++i) {
       const uint32_t s = i % kStages, ph = (i / kStages) & 1u;
       if (!dead && !mbar_wait(full0 + 8 * s, ph)) dead = true;
 
@@ -369,24 +419,6 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
           }
         }
         run_val += (double)tot.x + (double)tot.y;
-      } else if constexpr (SC >= 12) {
-        // Combine the slice totals of this tile across warps, under one barrier of the consumer
-        // warps.  Handing the totals to a collector warp through sequence-numbered slots, so that
-        // no consumer ever waits, measured slower (0.93 of the copy bandwidth at 4096, 8192 and
-        // 16384 elements against 1.01 / 0.97 / 0.95 with the barrier), as did letting the last
-        // warp to arrive do the adding.
-        if (lane == 0) part[i & 1][warp] = tot;
-        consumer_sync();
-        if (warp == 0) {
-          const float2 pr = part[i & 1][lane & 7];
-          double v = (double)pr.x + (double)pr.y;
-          constexpr int kWarpsPerSeg = SC == 12 ? 2 : (SC == 13 ? 4 : 8);
-#pragma unroll
-          for (int m = 1; m < kWarpsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-          const unsigned long long seg = tile * (8 / kWarpsPerSeg) + lane / kWarpsPerSeg;
-          if (lane < 8 && (lane % kWarpsPerSeg) == 0 && seg < p.num_segments && !dead)
-            store_seg(p.out, out_f32, seg, (float)v);
-        }
       }
     }
 
