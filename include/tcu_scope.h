@@ -47,7 +47,8 @@ typedef enum {
   TCU_ALGO_TCGEN05 = 3  /* tcgen05.mma, accumulators in tensor memory; powers of two,
                            num_elements % 64 == 0: segmented reduction of 16 ... 2048
                            elements (plain fp32 accumulation), inclusive segmented scan
-                           of 16 ... 16384 elements (exact parts, like TCU_ALGO_MMA)     */
+                           of 16 ... 16384 elements (exact parts, like TCU_ALGO_MMA),
+                           with 16-bit outputs of up to 2^20 elements (2 segments or more) */
 } tcu_algo;
 
 typedef enum { TCU_OUT_F16 = 0, TCU_OUT_F32 = 1 } tcu_out_type;

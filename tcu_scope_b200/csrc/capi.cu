@@ -444,8 +444,14 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   if (sc == kClassGeneral && algo != TCU_ALGO_AUTO && algo != TCU_ALGO_MMA) return TCU_ERR_UNSUPPORTED;
   size_t n = 0;
   if (mul_overflows(num_segments, segment_size, &n)) return TCU_ERR_INVALID_ARG;
-  // the tcgen05 variant: inclusive scans of 16 ... 16384-element segments of arrays it can view as 64-wide rows
-  if (algo == TCU_ALGO_TCGEN05 && (sc < 4 || sc > 14 || n % kSwizzleRowElems != 0 || exclusive))
+  // the tcgen05 variant: inclusive scans of 16 ... 16384-element segments of arrays it can view as
+  // 64-wide rows; with 16-bit outputs also whole segments of 2^15 ... 2^20 elements
+  int lg = 0;  // log2 of the segment size (powers of two)
+  while ((size_t(1) << lg) < segment_size) ++lg;
+  const bool spread_long = sc == kClassLong && num_segments > 1 && lg <= kUscanMaxLog2 &&
+                           out_type == TCU_OUT_F16 && shard_index == 0;
+  if (algo == TCU_ALGO_TCGEN05 &&
+      (sc < 4 || (sc > 14 && !spread_long) || n % kSwizzleRowElems != 0 || exclusive))
     return TCU_ERR_UNSUPPORTED;
   if (n == 0) return TCU_OK;
   if (!d_in || !d_out || !aligned16(d_in) || !aligned16(d_out)) return TCU_ERR_INVALID_ARG;
@@ -491,7 +497,7 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   const size_t umma_from = (f32 || sc >= 11) ? size_t(1) << 26 : size_t(1) << 27;
   const bool umma_auto = algo == TCU_ALGO_AUTO && !exclusive && n % kSwizzleRowElems == 0 &&
                          n >= umma_from && umma_class;
-  if (algo == TCU_ALGO_TCGEN05 || umma_auto) {
+  if ((algo == TCU_ALGO_TCGEN05 && sc <= 14) || umma_auto) {
     CUtensorMap omap;
     std::memset(&omap, 0, sizeof(omap));
     const bool maps = make_output_tensor_map(&omap, d_out, n, f32);
@@ -517,6 +523,31 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   if (sc == kClassLong) {
     const size_t need = scan_long_ws_bytes(n);
     if (!ws || ws_bytes < need || !aligned16(ws)) return TCU_ERR_WORKSPACE;
+    // 16-bit outputs of whole segments of up to 2^20 elements: the tcgen05 kernel spreads a segment
+    // over tiles like the 4096 ... 16384-element ones and needs no look-back (measured 0.84 ...
+    // 0.97 of the copy bandwidth at 2^28 elements where the look-back kernel reaches 0.67 ... 0.72;
+    // the workspace is then left untouched).  Work units are eight segments: taken only when they
+    // fill the SMs evenly enough.
+    if (spread_long && !exclusive && n % kSwizzleRowElems == 0 &&
+        (algo == TCU_ALGO_TCGEN05 || algo == TCU_ALGO_AUTO)) {
+      const size_t units  = (num_segments + 7) / 8;
+      const size_t rounds = (units + size_t(sms) - 1) / size_t(sms);
+      const bool even     = units * 100 >= rounds * size_t(sms) * 85;
+      CUtensorMap omap;
+      std::memset(&omap, 0, sizeof(omap));
+      if ((algo == TCU_ALGO_TCGEN05 || (even && n >= (size_t(1) << 26))) &&
+          make_output_tensor_map(&omap, d_out, n, false)) {
+        const int ugrid = units < size_t(sms) ? int(units) : sms;
+        switch (lg) {
+#define X(C) case C: e = launch_tcgen05_scan<C, false>(p, omap, ugrid, st); break;
+          X(15) X(16) X(17) X(18) X(19) X(20)
+#undef X
+          default: return TCU_ERR_UNSUPPORTED;
+        }
+        return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+      }
+      if (algo == TCU_ALGO_TCGEN05) return TCU_ERR_CUDA;
+    }
     uint8_t* w          = static_cast<uint8_t*>(ws);
     p.ticket            = reinterpret_cast<unsigned int*>(w);
     p.tile_status       = reinterpret_cast<unsigned long long*>(w + kWsHeader);

@@ -37,6 +37,7 @@ namespace TCU_NS {
 constexpr int kUscanRawStages   = 5;                   // 16 KiB tiles as the TMA copies deliver them (at most)
 constexpr int kUscanSplitStages = 2;                   // (hi, lo) tile pairs, 32 KiB each
 constexpr int kUscanAccStages   = 2;                   // accumulator pairs in tensor memory
+constexpr int kUscanMaxLog2     = 20;                  // longest segment (spread over 2^9 tiles)
 constexpr int kUscanN           = 64;                  // columns of U = outputs per row
 constexpr int kUscanBBytes      = kUscanN * 128;       // U, K-major: 64 rows of 64 halves
 constexpr int kUscanTmemCols    = kUscanAccStages * 2 * kUscanN;  // 256
@@ -111,7 +112,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, int c0, in
 template <int LOG2S, bool OUT32>
 __global__ void __launch_bounds__(512, 1)
     tcgen05_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap omap) {
-  static_assert(LOG2S >= 4 && LOG2S <= 14, "16 ... 16384 elements per segment");
+  static_assert(LOG2S >= 4 && LOG2S <= kUscanMaxLog2, "16 ... 2^20 elements per segment");
+  static_assert(LOG2S <= 14 || !OUT32, "segments longer than 16384 elements: 16-bit outputs only");
   constexpr int S = 1 << LOG2S;
   // Segments of more than 2048 elements (32 rows, what one epilogue warp reads of a tile) are
   // spread over G tiles so that one warp still sees a whole segment: a group is four consecutive

@@ -89,7 +89,10 @@ def test_tcgen05_scan_rejects_what_it_does_not_cover():
     import tcu_scope_b200 as tcu
     x = tcu.fill(torch.empty(1 << 15, dtype=torch.float16, device="cuda"), 1, 0)
     with pytest.raises(tcu.TcuError) as e:
-        tcu.segmented_scan(x, 32768, algo="tcgen05")  # only segments of 16 ... 16384 elements
+        tcu.segmented_scan(x, 32768, out_dtype=torch.float32, algo="tcgen05")  # fp32 outputs: up to 16384 elements
+    assert e.value.status == 2
+    with pytest.raises(tcu.TcuError) as e:
+        tcu.segmented_scan(x, 32768, out_dtype=torch.float16, algo="tcgen05")  # one segment is the full scan's job
     assert e.value.status == 2
     with pytest.raises(tcu.TcuError):
         tcu.segmented_scan(x[:4096 - 16], 16, algo="tcgen05")  # element count not a multiple of 64
@@ -112,3 +115,27 @@ def test_auto_runs_the_tcgen05_scan_on_large_arrays(s, out_dtype):
         assert bad == 0 and worst <= 1
     assert torch.equal(out, tcu.segmented_scan(x, s, out_dtype=out_dtype, algo="tcgen05"))
     assert tcu.device_error() == 0
+
+
+@pytest.mark.parametrize("s", [1 << 15, 1 << 16, 1 << 18, 1 << 20])
+def test_tcgen05_scan_of_long_segments_with_16bit_outputs(s):
+    """Whole segments of 2^15 ... 2^20 elements are spread over tiles like the 4096 ... 16384-element
+    ones: no look-back, no workspace traffic."""
+    import tcu_scope_b200 as tcu
+    for segs in (2, 3, 8, 9, 37):
+        n = s * segs
+        if n > 1 << 26:
+            continue
+        x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 300 + segs, 0)
+        buf = torch.full((n + 128,), -777.0, dtype=torch.float16, device="cuda")
+        out = buf[64:64 + n]
+        tcu.segmented_scan(x, s, out=out, algo="tcgen05")
+        bad, worst = oracle.np_check_f16(bits(out), oracle.c_segmented_scan(bits(x), s), 2)
+        assert bad == 0 and worst <= 1, (s, segs, worst)
+        guards = torch.cat([buf[:64], buf[64 + n:]]).float().cpu()
+        assert torch.all(guards == -777.0)
+        assert tcu.device_error() == 0
+    if s <= 1 << 16:  # sums beyond the exactly representable range (and still finite in fp16)
+        pos = tcu.fill(torch.empty(4 * s, dtype=torch.float16, device="cuda"), 6, 0, "uniform_01")
+        got = tcu.segmented_scan(pos, s, out_dtype=torch.float16, algo="tcgen05")
+        assert oracle.np_check_f16(bits(got), oracle.c_segmented_scan(bits(pos), s), 2)[0] == 0
