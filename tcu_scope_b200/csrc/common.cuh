@@ -50,7 +50,7 @@ constexpr unsigned kErrPeerTimeout     = 4u;  // a wait for another GPU's total 
 // wait gives up after roughly barrier * kWaitHintNs (about 2 s) instead of
 // hanging the device.  The limits live in device memory so that a test can
 // shorten them and make a wait run out within a millisecond; a kernel reads
-// them only after a first attempt has failed, never on its fast path.
+// them only after a few dozen attempts have failed, never on its fast path.
 constexpr uint32_t kWaitHintNs = 1000;
 struct WaitLimits {
   uint32_t barrier;  // mbarrier try_wait attempts
@@ -91,24 +91,44 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                : "memory");
 }
 
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait on a phase parity.  Returns false (after raising the error
-// word) when the phase never completed.
+// word) when the phase never completed.  The bound lives in global memory
+// and is fetched only after kFastAttempts attempts have failed: a fetch after
+// the first failed attempt put an L2 round trip between a barrier's
+// completion and the waiter noticing it, which cost the single-thread chains
+// of the tcgen05 reduction a fifth of their throughput.
+constexpr uint32_t kFastAttempts = 32;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  uint32_t limit = 1;  // the real bound is fetched once a first attempt has failed
-  for (uint32_t attempt = 0; attempt < limit; ++attempt) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
-        : "memory");
-    if (done) return true;
-    if (attempt == 0) limit = wait_limit(&g_wait_limits.barrier);
-  }
+#pragma unroll 1
+  for (uint32_t attempt = 0; attempt < kFastAttempts; ++attempt)
+    if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t limit = wait_limit(&g_wait_limits.barrier);
+#pragma unroll 1
+  for (uint32_t attempt = kFastAttempts; attempt < limit; ++attempt)
+    if (mbar_try_wait(bar, parity)) return true;
   raise_error(kErrBarrierTimeout);
   return false;
+}
+
+// The same wait for a thread that should not be too quick: after a first failed attempt it
+// sleeps `pace_ns` before it looks again.  A producer paced like this runs a little less far
+// ahead of the consumers than its ring would let it.
+__device__ __forceinline__ bool mbar_wait_paced(uint32_t bar, uint32_t parity, uint32_t pace_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  __nanosleep(pace_ns);
+  return mbar_wait(bar, parity);
 }
 
 // Linear TMA: global -> this CTA's shared memory, completion counted in bytes

@@ -129,18 +129,10 @@ __device__ __forceinline__ double look_back(const unsigned long long* status, lo
 __device__ __forceinline__ bool mbar_wait_or_stop(uint32_t bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag,
                                                   volatile uint32_t* end_index, uint32_t idx) {
-  uint32_t limit = 1;  // the real bound is fetched once a first attempt has failed
+  uint32_t limit = kFastAttempts;  // the real bound is fetched once these have failed
   for (uint32_t attempt = 0; attempt < limit; ++attempt) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(kWaitHintNs)
-        : "memory");
-    if (done) return true;
-    if (attempt == 0) limit = wait_limit(&g_wait_limits.barrier);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (attempt + 1 == kFastAttempts) limit = wait_limit(&g_wait_limits.barrier);
     if (*abort_flag) return false;
     if (end_index != nullptr && *end_index <= idx) return false;
   }

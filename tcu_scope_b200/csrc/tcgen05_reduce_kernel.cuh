@@ -27,8 +27,9 @@ namespace TCU_NS {
 constexpr int kUmmaRows       = 128;                               // rows (TMEM lanes) per tile
 constexpr int kUmmaTileElems  = kUmmaRows * kSwizzleRowElems;      // 8192 halves
 constexpr int kUmmaTileBytes  = kUmmaTileElems * 2;                // 16 KiB
-// Ring depth: 6 x 16 KiB in flight per SM measured fastest (1.03 of the copy
-// bandwidth at 2^28 elements); 8 stages give 0.98, 12 stages 0.90.
+// Ring depth: 3 / 4 / 6 / 8 / 12 stages of 16 KiB measured 0.74 / 0.80 / 0.79 / 0.79 / 0.78 of
+// the copy bandwidth at 2^28 elements (back-to-back launches; the mma.sync kernels: 1.04 ...
+// 1.07): the depth is not what holds this variant back.
 constexpr int kUmmaStages     = 6;
 constexpr int kUmmaN          = 16;                                // accumulator columns per tile
 constexpr int kUmmaBBytes     = kUmmaN * kSwizzleRowElems * 2;     // 2 KiB

@@ -34,7 +34,7 @@
 
 namespace TCU_NS {
 
-constexpr int kUscanRawStages   = 5;                   // 16 KiB tiles as the TMA copies deliver them (at most)
+constexpr int kUscanRawStages   = 4;                   // 16 KiB tiles as the TMA copies deliver them (at most)
 constexpr int kUscanSplitStages = 2;                   // (hi, lo) tile pairs, 32 KiB each
 constexpr int kUscanAccStages   = 2;                   // accumulator pairs in tensor memory
 constexpr int kUscanMaxLog2     = 20;                  // longest segment (spread over 2^9 tiles)
@@ -125,10 +125,10 @@ __global__ void __launch_bounds__(512, 1)
   constexpr int kRowsPerSeg  = S <= 64 ? 1 : (G > 1 ? 32 : S / 64);  // rows of a segment in a tile
   constexpr int kLanesPerSeg = kRowsPerSeg;
   // Depth of the input ring, measured at 2^28 elements (2 / 3 / 4 / 5 stages): fp32 outputs 0.90 /
-  // 0.96 / 0.89 / -- of the copy bandwidth at every segment size (reads that run far ahead get in
-  // the way of twice as many bytes of writes); 16-bit outputs 0.81 / 0.91 / 0.98 / 0.99 from 256
-  // elements on, and 0.81 / 0.91 / 0.98 / 0.90 for 16-element segments.
-  constexpr int NR = OUT32 ? 3 : (LOG2S == 4 ? 4 : kUscanRawStages);
+  // 0.95 / 0.88 / -- of the copy bandwidth at every segment size (reads that run far ahead get in
+  // the way of twice as many bytes of writes); 16-bit outputs -- / 0.93 / 1.00 / 0.89 at 256
+  // elements per segment, 0.88 / 0.98 / 0.88 at 4096, 0.93 / 0.95 / 0.87 at 16.
+  constexpr int NR = OUT32 ? 3 : kUscanRawStages;
   constexpr int NH = kUscanSplitStages, NA = kUscanAccStages;
   extern __shared__ uint8_t dyn_smem[];
   // raw_full | raw_empty | hl_full | hl_empty | acc_full | acc_empty
@@ -208,7 +208,12 @@ __global__ void __launch_bounds__(512, 1)
     if (lane == 0) {
       for (uint32_t i = 0; unit_of(i) < num_units; ++i) {
         const uint32_t s = i % NR, ph = (i / NR) & 1u;
-        if (!mbar_wait(raw_empty0 + 8 * s, ph ^ 1u)) { s_failed = 1u; break; }
+        // 16-element segments with 16-bit outputs measured best with a producer that does not
+        // refill a stage the instant it is free: 0.98 of the copy bandwidth at 2^28 elements with a
+        // pause of 500 ns or 1 us after a failed look, 0.94 with none or 250 ns, 0.91 with 2 us
+        const bool got = (LOG2S == 4 && !OUT32) ? mbar_wait_paced(raw_empty0 + 8 * s, ph ^ 1u, 500u)
+                                                : mbar_wait(raw_empty0 + 8 * s, ph ^ 1u);
+        if (!got) { s_failed = 1u; break; }
         // Linear copies (measured faster than a tensor-map copy; the split warps put the tile into
         // the layout the tensor core wants): 16 KiB of consecutive input, or one piece of 4 KiB
         // per quarter.  Behind the end of the array the stage keeps stale data: those rows only
