@@ -86,6 +86,22 @@ def test_other_algorithms_bf16(algo):
     assert tcu.device_error() == 0
 
 
+@pytest.mark.parametrize("s", [16, 64, 256, 2048, 4096, 16384, 65536])
+@pytest.mark.parametrize("out_dtype", [torch.float32, BF])
+def test_tcgen05_scan_bf16(s, out_dtype):
+    """The tensor-memory scan with bfloat16 inputs: single tiles, segments spread over tiles, and
+    (16-bit outputs) whole segments longer than 16384 elements."""
+    import tcu_scope_b200 as tcu
+    if s > 16384 and out_dtype == torch.float32:
+        pytest.skip("segments longer than 16384 elements: 16-bit outputs only")
+    n = s * max(3, (1 << 20) // s + 5)
+    n = (n + 63) // 64 * 64 if s < 64 else n  # whole 64-element rows
+    x = tcu.fill(torch.empty(n, dtype=BF, device="cuda"), 500 + s, 0)
+    out = tcu.segmented_scan(x, s, out_dtype=out_dtype, algo="tcgen05")
+    check(out, oracle.np_segmented_scan(bits(x), s, fmt="bf16"))
+    assert tcu.device_error() == 0
+
+
 def test_exact_cases_bf16():
     import tcu_scope_b200 as tcu
     ones = torch.ones(1 << 16, dtype=BF, device="cuda")
