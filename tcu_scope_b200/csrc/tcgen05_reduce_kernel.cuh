@@ -27,9 +27,10 @@ namespace TCU_NS {
 constexpr int kUmmaRows       = 128;                               // rows (TMEM lanes) per tile
 constexpr int kUmmaTileElems  = kUmmaRows * kSwizzleRowElems;      // 8192 halves
 constexpr int kUmmaTileBytes  = kUmmaTileElems * 2;                // 16 KiB
-// Ring depth: 3 / 4 / 6 / 8 / 12 stages of 16 KiB measured 0.74 / 0.80 / 0.79 / 0.79 / 0.78 of
-// the copy bandwidth at 2^28 elements (back-to-back launches; the mma.sync kernels: 1.04 ...
-// 1.07): the depth is not what holds this variant back.
+// Ring depth: 3 / 4 / 6 / 8 / 10 stages of 16 KiB measured 0.75-0.85 / 0.84-0.92 / 0.90 /
+// 0.88-0.92 / 0.84-0.91 of the copy bandwidth at 2^28 elements (back-to-back launches, segment
+// sizes 16 ... 2048; the mma.sync kernels: 0.91 ... 1.05 in the same run): the depth is not what
+// holds this variant at 0.9.
 constexpr int kUmmaStages     = 6;
 constexpr int kUmmaN          = 16;                                // accumulator columns per tile
 constexpr int kUmmaBBytes     = kUmmaN * kSwizzleRowElems * 2;     // 2 KiB
