@@ -393,8 +393,8 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   if (algo == TCU_ALGO_TCGEN05) {
     CUtensorMap map;
     std::memset(&map, 0, sizeof(map));
-    if (!make_input_tensor_map(&map, d_in, n, kUmmaRows)) return TCU_ERR_CUDA;
-    const size_t utiles = (n + kUmmaTileElems - 1) / kUmmaTileElems;
+    if (!make_input_tensor_map(&map, d_in, n, kUmmaPerStage * kUmmaRows)) return TCU_ERR_CUDA;
+    const size_t utiles = (n + kUmmaPerStage * kUmmaTileElems - 1) / (kUmmaPerStage * kUmmaTileElems);
     const int ugrid     = utiles < size_t(sms) ? int(utiles) : sms;
     switch (sc) {
 #define X(C) case C: e = launch_tcgen05_reduce<C>(p, map, ugrid, st); break;

@@ -15,7 +15,7 @@
 //   D (128 lanes x 16 fp32 columns of TMEM), a ring of accumulators deep enough
 //       to hide the MMA -> commit -> tcgen05.ld -> release round trip.
 //
-// Warps: 0 TMA producer, 1 MMA issuer (and TMEM owner), 2..5 epilogue.  Every
+// Warps: 0 TMA producer, 1 MMA issuer (and TMEM owner), 2..9 epilogue (two sets).  Every
 // mbarrier wait is bounded; TMEM is released on every path out of the kernel.
 #pragma once
 
@@ -27,19 +27,27 @@ namespace TCU_NS {
 constexpr int kUmmaRows       = 128;                               // rows (TMEM lanes) per tile
 constexpr int kUmmaTileElems  = kUmmaRows * kSwizzleRowElems;      // 8192 halves
 constexpr int kUmmaTileBytes  = kUmmaTileElems * 2;                // 16 KiB
-// Ring depth: 3 / 4 / 6 / 8 / 10 stages of 16 KiB measured 0.75-0.85 / 0.84-0.92 / 0.90 /
-// 0.88-0.92 / 0.84-0.91 of the copy bandwidth at 2^28 elements (back-to-back launches, segment
-// sizes 16 ... 2048; the mma.sync kernels: 0.91 ... 1.05 in the same run): the depth is not what
-// holds this variant at 0.9.
-constexpr int kUmmaStages     = 6;
+// Ring: stages of TWO tiles (32 KiB, one tensor-map copy, one round of barrier operations for
+// the producer and the issuer thread), 3 of them.  With stages of one tile this variant stayed at
+// 0.90 of the copy bandwidth whatever the depth (3 ... 12 stages), the form of the copy (linear
+// or tensor map) or the number of epilogue warps: a kernel that only reads turns tiles over
+// twice as fast as a scan, and the single-thread chains of barrier operations set the pace.
+// Measured at 2^28 elements with 2 / 3 / 4 / 6 stages of two tiles: 0.87-0.93 / 0.96-1.02 /
+// 0.95-1.00 / 0.88-0.92 (segment sizes 64 ... 2048; 16-element segments 0.81 / 0.89 / 0.89 / 0.83,
+// bound by their 4 bytes written per 32 read like the mma.sync kernel's 0.92 in the same run).
+constexpr int kUmmaStages     = 3;
+constexpr int kUmmaPerStage   = 2;                                 // tiles a ring stage holds
+constexpr int kUmmaStageBytes = kUmmaPerStage * kUmmaTileBytes;    // 32 KiB, one tensor-map copy
 constexpr int kUmmaN          = 16;                                // accumulator columns per tile
 constexpr int kUmmaBBytes     = kUmmaN * kSwizzleRowElems * 2;     // 2 KiB
-constexpr int kUmmaThreads    = 6 * 32;
+constexpr int kUmmaEpiSets    = 2;  // sets of four epilogue warps that take alternate stages
+constexpr int kUmmaThreads    = (2 + 4 * kUmmaEpiSets) * 32;
 constexpr int kUmmaAccStages  = 4;              // accumulators in flight (power of two)
-constexpr int kUmmaTmemCols   = kUmmaAccStages * kUmmaN < 32 ? 32 : kUmmaAccStages * kUmmaN;
+constexpr int kUmmaAccCols    = kUmmaPerStage * kUmmaN;            // accumulator columns of one stage
+constexpr int kUmmaTmemCols   = kUmmaAccStages * kUmmaAccCols < 32 ? 32 : kUmmaAccStages * kUmmaAccCols;
 static_assert((kUmmaAccStages & (kUmmaAccStages - 1)) == 0 && kUmmaTmemCols <= 512 &&
               (kUmmaTmemCols & (kUmmaTmemCols - 1)) == 0, "TMEM columns: a power of two, 32..512");
-constexpr int kUmmaDynSmemBytes = kUmmaStages * kUmmaTileBytes + kUmmaBBytes + 1024;
+constexpr int kUmmaDynSmemBytes = kUmmaStages * kUmmaStageBytes + kUmmaBBytes + 1024;
 
 // 64-bit shared-memory matrix descriptor, K-major, 128-byte swizzle: start
 // address and offsets in 16-byte units; rows of one 8-row group are 128 bytes
@@ -93,7 +101,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   __shared__ uint32_t s_failed;
 
   uint8_t* tiles = dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u);
-  uint8_t* bmat  = tiles + kUmmaStages * kUmmaTileBytes;  // 1 KiB aligned as well
+  uint8_t* bmat  = tiles + kUmmaStages * kUmmaStageBytes;  // 1 KiB aligned as well
   const uint32_t tiles_u32 = smem_u32(tiles), bmat_u32 = smem_u32(bmat);
   const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kUmmaStages]);
   const uint32_t tfull0 = smem_u32(&bars[2 * kUmmaStages]), tempty0 = tfull0 + 8 * kUmmaAccStages;
@@ -116,11 +124,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       // in flight while the others build B and allocate tensor memory.
       pdl_prologue();
       const unsigned long long rows  = p.num_elems / kSwizzleRowElems;
-      const unsigned long long tiles = (rows + kUmmaRows - 1) / kUmmaRows;
+      const unsigned long long tiles = (rows + kUmmaPerStage * kUmmaRows - 1) / (kUmmaPerStage * kUmmaRows);
       unsigned long long tile = blockIdx.x;
       for (int s = 0; s < kUmmaStages && tile < tiles; ++s, tile += gridDim.x) {
-        mbar_arrive_expect_tx(full0 + 8 * s, kUmmaTileBytes);
-        tma_load_2d(tiles_u32 + s * kUmmaTileBytes, &tmap, 0, (int)(tile * kUmmaRows), full0 + 8 * s);
+        mbar_arrive_expect_tx(full0 + 8 * s, kUmmaStageBytes);
+        tma_load_2d(tiles_u32 + s * kUmmaStageBytes, &tmap, 0, (int)(tile * kUmmaPerStage * kUmmaRows),
+                    full0 + 8 * s);
       }
     }
   }
@@ -145,7 +154,11 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const uint32_t tmem_base = s_tmem_base;
 
   const unsigned long long num_rows  = p.num_elems / kSwizzleRowElems;
-  const unsigned long long num_tiles = (num_rows + kUmmaRows - 1) / kUmmaRows;
+  // A ring stage, and a step of every role, is kUmmaPerStage tiles: with single tiles the chains
+  // of barrier operations of the producer and issuer threads, not HBM, set the pace of a kernel
+  // that only reads (0.90 of the copy bandwidth whatever the ring depth or the copy's form).
+  const unsigned long long num_tiles =
+      (num_rows + kUmmaPerStage * kUmmaRows - 1) / (kUmmaPerStage * kUmmaRows);
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -156,8 +169,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
            tile += gridDim.x, ++i) {
         const uint32_t s = i % kUmmaStages, ph = (i / kUmmaStages) & 1u;
         if (!mbar_wait(empty0 + 8 * s, ph ^ 1u)) { s_failed = 1u; break; }
-        mbar_arrive_expect_tx(full0 + 8 * s, kUmmaTileBytes);  // rows past the end arrive as zeros
-        tma_load_2d(tiles_u32 + s * kUmmaTileBytes, &tmap, 0, (int)(tile * kUmmaRows),
+        mbar_arrive_expect_tx(full0 + 8 * s, kUmmaStageBytes);  // rows past the end arrive as zeros
+        tma_load_2d(tiles_u32 + s * kUmmaStageBytes, &tmap, 0, (int)(tile * kUmmaPerStage * kUmmaRows),
                     full0 + 8 * s);
       }
     }
@@ -171,11 +184,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         if (!mbar_wait(tempty0 + 8 * a, aph ^ 1u)) { s_failed = 1u; break; }  // accumulator drained
         if (!mbar_wait(full0 + 8 * s, ph)) { s_failed = 1u; break; }          // tile landed
         tcgen05_fence_after_sync();
-        const uint32_t a_addr = tiles_u32 + s * kUmmaTileBytes;
+        const uint32_t a_addr = tiles_u32 + s * kUmmaStageBytes;
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb)  // K = 64 halves in four steps of 16 (32 bytes)
-          umma_f16(tmem_base + a * kUmmaN, umma_smem_desc(a_addr + 32 * kb),
-                   umma_smem_desc(bmat_u32 + 32 * kb), kb > 0 ? 1u : 0u);
+        for (int h = 0; h < kUmmaPerStage; ++h)
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)  // K = 64 halves in four steps of 16 (32 bytes)
+            umma_f16(tmem_base + a * kUmmaAccCols + h * kUmmaN,
+                     umma_smem_desc(a_addr + h * kUmmaTileBytes + 32 * kb),
+                     umma_smem_desc(bmat_u32 + 32 * kb), kb > 0 ? 1u : 0u);
         umma_commit(empty0 + 8 * s);   // the stage may be refilled once these MMAs have read it
         umma_commit(tfull0 + 8 * a);   // ... and the epilogue may read the accumulator
       }
@@ -184,47 +200,53 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
     const bool out_f32 = p.out_is_f32 != 0;
-    uint32_t i = 0;
-    for (unsigned long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++i) {
+    uint32_t i = (warp - 2) / 4;  // this warp's set: tiles i, i + kUmmaEpiSets, ... of the CTA
+    for (unsigned long long tile = blockIdx.x + (unsigned long long)i * gridDim.x; tile < num_tiles;
+         tile += (unsigned long long)kUmmaEpiSets * gridDim.x, i += kUmmaEpiSets) {
       const uint32_t a = i % kUmmaAccStages, aph = (i / kUmmaAccStages) & 1u;
       if (!mbar_wait(tfull0 + 8 * a, aph)) { s_failed = 1u; break; }
       tcgen05_fence_after_sync();
-      uint32_t r0, r1, r2, r3;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kUmmaN;
-      asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr) : "memory");
+      uint32_t r[kUmmaPerStage][4];
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * kUmmaAccCols;
+#pragma unroll
+      for (int h = 0; h < kUmmaPerStage; ++h)
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r[h][0]), "=r"(r[h][1]), "=r"(r[h][2]), "=r"(r[h][3])
+                     : "r"(taddr + h * kUmmaN) : "memory");
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * a);  // values are in registers now
-      const unsigned long long row = tile * kUmmaRows + quarter * 32 + lane;
-      if constexpr (kRowsPerSeg > 1) {
-        // a segment is kRowsPerSeg consecutive rows = consecutive lanes of this warp: add the row
-        // sums up in double (rows past the end of the array are zeros and join harmlessly)
-        double v = static_cast<double>(__uint_as_float(r0));
 #pragma unroll
-        for (int m = 1; m < kRowsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
-        const unsigned long long seg = row / kRowsPerSeg;
-        if ((lane & (kRowsPerSeg - 1)) == 0 && seg < p.num_segments)
-          store_seg(p.out, out_f32, seg, static_cast<float>(v));
-        continue;
-      }
-      const unsigned long long seg = row * kSegsPerRow;
-      if (seg < p.num_segments) {  // rows past the end of the array hold zeros: not stored
-        const float v0 = __uint_as_float(r0), v1 = __uint_as_float(r1);
-        const float v2 = __uint_as_float(r2), v3 = __uint_as_float(r3);
-        if constexpr (kSegsPerRow == 4) {
-          if (out_f32) {
-            *reinterpret_cast<float4*>(static_cast<float*>(p.out) + seg) = make_float4(v0, v1, v2, v3);
-          } else {
-            *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + seg) =
-                make_uint2(pack2_rn(v0, v1), pack2_rn(v2, v3));
-          }
-        } else if constexpr (kSegsPerRow == 2) {
-          store_seg(p.out, out_f32, seg, v0);
-          store_seg(p.out, out_f32, seg + 1, v1);
+      for (int h = 0; h < kUmmaPerStage; ++h) {
+        const unsigned long long row = (tile * kUmmaPerStage + h) * kUmmaRows + quarter * 32 + lane;
+        if constexpr (kRowsPerSeg > 1) {
+          // a segment is kRowsPerSeg consecutive rows = consecutive lanes of this warp: add the row
+          // sums up (rows past the end of the array are zeros and join harmlessly)
+          float v = __uint_as_float(r[h][0]);
+#pragma unroll
+          for (int m = 1; m < kRowsPerSeg; m <<= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+          const unsigned long long seg = row / kRowsPerSeg;
+          if ((lane & (kRowsPerSeg - 1)) == 0 && seg < p.num_segments) store_seg(p.out, out_f32, seg, v);
         } else {
-          store_seg(p.out, out_f32, seg, v0);
+          const unsigned long long seg = row * kSegsPerRow;
+          if (seg < p.num_segments) {  // rows past the end of the array hold zeros: not stored
+            const float v0 = __uint_as_float(r[h][0]), v1 = __uint_as_float(r[h][1]);
+            const float v2 = __uint_as_float(r[h][2]), v3 = __uint_as_float(r[h][3]);
+            if constexpr (kSegsPerRow == 4) {
+              if (out_f32) {
+                *reinterpret_cast<float4*>(static_cast<float*>(p.out) + seg) = make_float4(v0, v1, v2, v3);
+              } else {
+                *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.out) + seg) =
+                    make_uint2(pack2_rn(v0, v1), pack2_rn(v2, v3));
+              }
+            } else if constexpr (kSegsPerRow == 2) {
+              store_seg(p.out, out_f32, seg, v0);
+              store_seg(p.out, out_f32, seg + 1, v1);
+            } else {
+              store_seg(p.out, out_f32, seg, v0);
+            }
+          }
         }
       }
     }
