@@ -487,14 +487,14 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   // TCU_ALGO_AUTO takes the tcgen05 kernel where it measured faster than the mma.sync one:
-  // 16-bit outputs of 16- and 256 ... 16384-element segments (0.97 ... 0.98 of the copy bandwidth
-  // at 2^28 elements against 0.92 / 0.93 ... 0.76) and fp32 outputs of 16-element segments (0.95
-  // against 0.91).  Its set-up costs 3-4 us more, so it takes over from 2^26 elements on for
-  // 16-bit outputs of segments of 2048 and more (47.6 against 54.4 us at 4096) and for the fp32
-  // case (68.5 against 73.1 us), and from 2^27 on for the shorter 16-bit ones (a tie at 2^26, 87.7
-  // against 91.1 us at 2^27 and 16-element segments).
+  // 16-bit outputs of 16- and 256 ... 16384-element segments (0.96 ... 1.00 of the copy bandwidth
+  // at 2^28 elements against 0.92 / 0.94 ... 0.76) and fp32 outputs of 16-element segments (0.94
+  // against 0.89).  Its set-up costs 2-3 us more, so it takes over from 2^25 elements on for
+  // 16-bit outputs of segments of 4096 and more (27.2 against 29.4 us at 4096) and from 2^26 on
+  // for the others (16-bit: 45.8 against 47.5 us at 16 elements, 45.6 against 46.9 at 256;
+  // fp32: 68.6 against 72.6 us; at 2^25 the mma.sync kernels win 20.7 ... 25.6 against 27 us).
   const bool umma_class = f32 ? sc == 4 : (sc == 4 || (sc >= 8 && sc <= 14));
-  const size_t umma_from = (f32 || sc >= 11) ? size_t(1) << 26 : size_t(1) << 27;
+  const size_t umma_from = (!f32 && sc >= 12) ? size_t(1) << 25 : size_t(1) << 26;
   const bool umma_auto = algo == TCU_ALGO_AUTO && !exclusive && n % kSwizzleRowElems == 0 &&
                          n >= umma_from && umma_class;
   if ((algo == TCU_ALGO_TCGEN05 && sc <= 14) || umma_auto) {

@@ -167,6 +167,42 @@ __global__ void __launch_bounds__(512, 1)
     }
   };
 
+  // Requests the CTA's i-th tile into its ring stage (one thread).
+  auto issue_tile = [&](uint32_t i) {
+    const uint32_t s = i % NR;
+    // Linear copies (measured faster than a tensor-map copy; the split warps put the tile into
+    // the layout the tensor core wants): 16 KiB of consecutive input, or one piece of 4 KiB
+    // per quarter.  Behind the end of the array the stage keeps stale data: those rows only
+    // feed rows after them, and none of these is stored.
+    const uint32_t dst = raw_u32 + s * kUmmaTileBytes, bar = raw_full0 + 8 * s;
+    if constexpr (G == 1) {
+      const unsigned long long row = quarter_row(i, 0);
+      if (row >= num_rows) {
+        mbar_arrive(bar);
+      } else {
+        const unsigned long long rem = (num_rows - row) * 128ull;
+        const uint32_t bytes = rem < (unsigned long long)kUmmaTileBytes ? (uint32_t)rem : kUmmaTileBytes;
+        mbar_arrive_expect_tx(bar, bytes);
+        tma_load_1d(dst, p.in + row * 128ull, bytes, bar);
+      }
+    } else {
+      // whole segments only: a quarter's 32 rows are all inside the array or all outside
+      uint32_t pieces = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) pieces += quarter_row(i, q) < num_rows ? 1u : 0u;
+      if (pieces == 0) {
+        mbar_arrive(bar);
+      } else {
+        mbar_arrive_expect_tx(bar, pieces * 4096u);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const unsigned long long row = quarter_row(i, q);
+          if (row < num_rows) tma_load_1d(dst + q * 4096u, p.in + row * 128ull, 4096u, bar);
+        }
+      }
+    }
+  };
+
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&omap)) : "memory");
     for (int s = 0; s < NR; ++s) {
@@ -183,6 +219,10 @@ __global__ void __launch_bounds__(512, 1)
     }
     s_failed = 0u;
     mbar_fence_init();
+    // This thread is also the producer: it fills the ring right away, so that the first tiles are
+    // in flight while the others build U and allocate tensor memory.
+    pdl_prologue();
+    for (uint32_t i = 0; i < (uint32_t)NR && unit_of(i) < num_units; ++i) issue_tile(i);
   }
   // U restricted to the segments inside a row: B[n][k] = 1 iff k <= n and both in one segment.
   for (int idx = threadIdx.x; idx < kUscanN * kSwizzleRowElems; idx += kUscanThreads) {
@@ -206,7 +246,8 @@ __global__ void __launch_bounds__(512, 1)
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      for (uint32_t i = 0; unit_of(i) < num_units; ++i) {
+      // the first NR tiles were requested before the CTA-wide set-up (see above)
+      for (uint32_t i = NR; unit_of(i) < num_units; ++i) {
         const uint32_t s = i % NR, ph = (i / NR) & 1u;
         // 16-element segments with 16-bit outputs measured best with a producer that does not
         // refill a stage the instant it is free: 0.98 of the copy bandwidth at 2^28 elements with a
@@ -214,37 +255,7 @@ __global__ void __launch_bounds__(512, 1)
         const bool got = (LOG2S == 4 && !OUT32) ? mbar_wait_paced(raw_empty0 + 8 * s, ph ^ 1u, 500u)
                                                 : mbar_wait(raw_empty0 + 8 * s, ph ^ 1u);
         if (!got) { s_failed = 1u; break; }
-        // Linear copies (measured faster than a tensor-map copy; the split warps put the tile into
-        // the layout the tensor core wants): 16 KiB of consecutive input, or one piece of 4 KiB
-        // per quarter.  Behind the end of the array the stage keeps stale data: those rows only
-        // feed rows after them, and none of these is stored.
-        const uint32_t dst = raw_u32 + s * kUmmaTileBytes, bar = raw_full0 + 8 * s;
-        if constexpr (G == 1) {
-          const unsigned long long row = quarter_row(i, 0);
-          if (row >= num_rows) {
-            mbar_arrive(bar);
-          } else {
-            const unsigned long long rem = (num_rows - row) * 128ull;
-            const uint32_t bytes = rem < (unsigned long long)kUmmaTileBytes ? (uint32_t)rem : kUmmaTileBytes;
-            mbar_arrive_expect_tx(bar, bytes);
-            tma_load_1d(dst, p.in + row * 128ull, bytes, bar);
-          }
-        } else {
-          // whole segments only: a quarter's 32 rows are all inside the array or all outside
-          uint32_t pieces = 0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) pieces += quarter_row(i, q) < num_rows ? 1u : 0u;
-          if (pieces == 0) {
-            mbar_arrive(bar);
-          } else {
-            mbar_arrive_expect_tx(bar, pieces * 4096u);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const unsigned long long row = quarter_row(i, q);
-              if (row < num_rows) tma_load_1d(dst + q * 4096u, p.in + row * 128ull, 4096u, bar);
-            }
-          }
-        }
+        issue_tile(i);
       }
     }
   } else if (warp == 1) {
