@@ -384,10 +384,19 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   if (sc == kClassGeneral) {
-    e = launch_pdl(segment_size % 8 == 0 ? seg_reduce_general_kernel<true>
-                                         : seg_reduce_general_kernel<false>,
-                   p, (unsigned long long)segment_size, general_grid(num_segments, sms),
-                   kGeneralThreads, 0, st);
+    // one warp per segment, or -- when that leaves SMs idle and the segments are long -- one CTA
+    const bool vec   = segment_size % 8 == 0;
+    const bool block = segment_size >= 8192 && num_segments < size_t(sms) * 32;
+    if (block) {
+      const size_t cap = size_t(sms) * 8;
+      e = launch_pdl(vec ? seg_reduce_general_kernel<true, true> : seg_reduce_general_kernel<false, true>, p,
+                     (unsigned long long)segment_size, int(num_segments < cap ? num_segments : cap),
+                     kGeneralThreads, 0, st);
+    } else {
+      e = launch_pdl(vec ? seg_reduce_general_kernel<true> : seg_reduce_general_kernel<false>, p,
+                     (unsigned long long)segment_size, general_grid(num_segments, sms), kGeneralThreads,
+                     0, st);
+    }
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   if (algo == TCU_ALGO_TCGEN05) {

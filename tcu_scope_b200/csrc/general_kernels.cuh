@@ -56,15 +56,20 @@ __device__ __forceinline__ void store_masked(void* out, unsigned long long idx, 
 // element lands in exactly one row sum, whichever row that is.  Row sums of
 // the exact hi and lo parts are flushed into a compensated pair of floats before they can
 // round (double arithmetic is slow on this part).
-template <bool kVec>
+// kBlock: long segments, too few of them to keep the SMs busy with one warp each -- the eight
+// warps of a CTA share a segment (each takes every eighth run of 128 vectors) and their sums
+// meet in shared memory.
+template <bool kVec, bool kBlock = false>
 __global__ void __launch_bounds__(kGeneralThreads) seg_reduce_general_kernel(const ReduceParams p,
                                                              unsigned long long seg_elems) {
   pdl_prologue();
-  const int lane = threadIdx.x & 31;
-  const unsigned long long warps = (unsigned long long)gridDim.x * (kGeneralThreads / 32);
-  const unsigned long long first =
-      (unsigned long long)blockIdx.x * (kGeneralThreads / 32) + (threadIdx.x >> 5);
+  constexpr int kWarps = kGeneralThreads / 32;
+  __shared__ float2 warp_tot[kWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned long long warps = kBlock ? gridDim.x : (unsigned long long)gridDim.x * kWarps;
+  const unsigned long long first = kBlock ? blockIdx.x : (unsigned long long)blockIdx.x * kWarps + warp;
   const unsigned long long vecs  = (seg_elems + 7) / 8;  // groups of 8 elements per segment
+  const unsigned long long v_first = kBlock ? 128ull * warp : 0ull, v_step = kBlock ? 128ull * kWarps : 128ull;
   const Acc zero{0.f, 0.f, 0.f, 0.f};
   constexpr int kFlushEvery = 64;  // 64 steps x 16 elements per row: sums below 2^11 stay exact
 
@@ -73,26 +78,36 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_reduce_general_kernel(con
     float tot_h = 0.f, tot_l = 0.f;
     Acc ah = zero, al = zero;
     int pending = 0;
-    for (unsigned long long v0 = 0; v0 < vecs; v0 += 32) {
-      const unsigned long long v = v0 + lane;
-      uint4 x = make_uint4(0u, 0u, 0u, 0u);
-      if (v < vecs) {
-        if constexpr (kVec) {
-          x = ldg128(src + v * 16);
-        } else {
-          uint32_t w[4];
-          ldg_halves_masked<8>(src + v * 16, (long long)(seg_elems - v * 8), w);
-          x = make_uint4(w[0], w[1], w[2], w[3]);
+    // four vectors per lane in flight: a lone warp per segment has nothing else to hide the
+    // latency of its loads with
+    for (unsigned long long v0 = v_first; v0 < vecs; v0 += v_step) {
+      uint4 x[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const unsigned long long v = v0 + 32u * k + lane;
+        x[k] = make_uint4(0u, 0u, 0u, 0u);
+        if (v < vecs) {
+          if constexpr (kVec) {
+            x[k] = ldg128(src + v * 16);
+          } else {
+            uint32_t w[4];
+            ldg_halves_masked<8>(src + v * 16, (long long)(seg_elems - v * 8), w);
+            x[k] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
         }
       }
-      uint32_t h[4], l[4];
-      split_hi_lo(x.x, h[0], l[0]);
-      split_hi_lo(x.y, h[1], l[1]);
-      split_hi_lo(x.z, h[2], l[2]);
-      split_hi_lo(x.w, h[3], l[3]);
-      ah = mma_ones(h, ah);
-      al = mma_ones(l, al);
-      if (++pending == kFlushEvery) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint32_t h[4], l[4];
+        split_hi_lo(x[k].x, h[0], l[0]);
+        split_hi_lo(x[k].y, h[1], l[1]);
+        split_hi_lo(x[k].z, h[2], l[2]);
+        split_hi_lo(x[k].w, h[3], l[3]);
+        ah = mma_ones(h, ah);
+        al = mma_ones(l, al);
+      }
+      pending += 4;
+      if (pending >= kFlushEvery) {
         pair_add(tot_h, tot_l, ah.d0, al.d0);
         pair_add(tot_h, tot_l, ah.d2, al.d2);
         ah = al = zero;
@@ -106,6 +121,17 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_reduce_general_kernel(con
     for (int off = 4; off <= 16; off <<= 1) {
       const float oh = __shfl_xor_sync(0xffffffffu, tot_h, off), ol = __shfl_xor_sync(0xffffffffu, tot_l, off);
       pair_add(tot_h, tot_l, oh, ol);
+    }
+    if constexpr (kBlock) {
+      if (lane == 0) warp_tot[warp] = make_float2(tot_h, tot_l);
+      __syncthreads();
+      if (warp == 0) {
+        tot_h = tot_l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) pair_add(tot_h, tot_l, warp_tot[w].x, warp_tot[w].y);
+      }
+      __syncthreads();  // warp_tot is written again for the CTA's next segment
+      if (warp != 0) continue;
     }
     if (lane == 0) {
       store_seg(p.out, p.out_is_f32 != 0, seg, tot_h + tot_l);
@@ -137,12 +163,12 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
   for (unsigned long long seg = first; seg < num_segments; seg += warps) {
     const unsigned long long seg_base = seg * seg_elems;
     float xh = 0.f, xl = 0.f;  // the segment so far: an exact multiple of 2^-13 plus a small rest
-    for (unsigned long long e0 = 0; e0 < seg_elems; e0 += 256) {
+    // this lane's elements of step e0: four of row g, four of row g + 8 (zeros past the segment's end)
+    auto load_step = [&](unsigned long long e0, uint2& lo, uint2& hi) {
+      lo = hi = make_uint2(0u, 0u);
+      if (e0 >= seg_elems) return;
       const uint8_t* src = p.in + (seg_base + e0) * 2ull;
-      const long long left = (long long)(seg_elems - e0);  // elements of the segment from this step on
-      // this lane's four elements of row g / row g+8: how many of them exist
-      const long long n_lo = left - off_lo / 2, n_hi = n_lo - Geom::kHiOffset / 2;
-      uint2 lo = make_uint2(0u, 0u), hi = make_uint2(0u, 0u);
+      const long long n_lo = (long long)(seg_elems - e0) - off_lo / 2, n_hi = n_lo - Geom::kHiOffset / 2;
       if constexpr (kVec) {  // whole groups of four
         if (n_lo > 0) lo = ldg64(src + off_lo);
         if (n_hi > 0) hi = ldg64(src + off_lo + Geom::kHiOffset);
@@ -153,6 +179,19 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_scan_general_kernel(const
         ldg_halves_masked<4>(src + off_lo + Geom::kHiOffset, n_hi, w);
         hi = make_uint2(w[0], w[1]);
       }
+    };
+    // the loads of the next two steps are in flight while one step is worked on
+    uint2 lo1, hi1, lo2, hi2;
+    load_step(0, lo1, hi1);
+    load_step(256, lo2, hi2);
+    for (unsigned long long e0 = 0; e0 < seg_elems; e0 += 256) {
+      const long long left = (long long)(seg_elems - e0);  // elements of the segment from this step on
+      // this lane's four elements of row g / row g+8: how many of them exist
+      const long long n_lo = left - off_lo / 2, n_hi = n_lo - Geom::kHiOffset / 2;
+      const uint2 lo = lo1, hi = hi1;
+      lo1 = lo2;
+      hi1 = hi2;
+      load_step(e0 + 512, lo2, hi2);
       uint32_t ah[4], al[4];
       split_hi_lo(lo.x, ah[0], al[0]);
       split_hi_lo(hi.x, ah[1], al[1]);
