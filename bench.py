@@ -736,6 +736,54 @@ def cub_leg(torch, tcu, args):
     return out
 
 
+def adjacent_sizes_leg(torch, tcu, args, peak_gbs):
+    """Segment sizes next to the benchmark definition's: multiples of 8 / 16 that are not powers of
+    two (the reference's 16n kernels accept the latter) and whole segments longer than 16384
+    elements with 16-bit outputs.  Fractions of the measured copy bandwidth."""
+    n_max = 1 << min(args.log2_elems, 28)
+    xs = [tcu.fill(torch.empty(n_max, dtype=torch.float16, device="cuda"), 77 + i, 0) for i in range(2)]
+    k = [0]
+
+    def timed(fn, bytes_moved):
+        ms, _ = time_op(torch, fn, 8, 3)
+        return round(bytes_moved / ms / 1e6 / peak_gbs, 3)
+
+    out = {"unit": "fraction of the measured copy bandwidth", "reduce_f32": {}, "scan_f32": {},
+           "scan_f16": {}, "scan_f16_long_segments": {}}
+    for s in (48, 240, 1000, 2000):
+        n = n_max // s * s
+        o = torch.empty(n // s, dtype=torch.float32, device="cuda")
+
+        def red():
+            k[0] += 1
+            tcu.segmented_reduce(xs[k[0] % 2][:n], s, out=o)
+        out["reduce_f32"][str(s)] = timed(red, n * 2 + n // s * 4)
+        if s % 16:
+            continue
+        for dt, key, width in ((torch.float32, "scan_f32", 4), (torch.float16, "scan_f16", 2)):
+            o2 = torch.empty(n, dtype=dt, device="cuda")
+
+            def scan():
+                k[0] += 1
+                tcu.segmented_scan(xs[k[0] % 2][:n], s, out=o2)
+            out[key][str(s)] = timed(scan, n * (2 + width))
+            del o2
+    o16 = torch.empty(n_max, dtype=torch.float16, device="cuda")
+    for lg in (15, 16, 17, 18):
+        s = 1 << lg
+        if n_max // s < 2:
+            continue
+        ws = torch.empty(tcu.workspace_bytes(tcu.OP_SEGMENTED_SCAN, n_max, s), dtype=torch.uint8, device="cuda")
+        row = {}
+        for algo in ("auto", "mma"):  # mma: the single-pass look-back kernel
+            def scan():
+                k[0] += 1
+                tcu.segmented_scan(xs[k[0] % 2], s, out=o16, algo=algo, workspace=ws)
+            row[algo] = timed(scan, n_max * 4)
+        out["scan_f16_long_segments"][f"2^{lg}"] = row
+    return out
+
+
 def ablation_leg(torch, tcu, args):
     """In-run ablation: the same TMA pipeline with CUDA-core adds and warp shuffles in place of
     the tensor-core contraction (TCU_ALGO_SHUFFLE), on the sweep and on the segmented scans, and
@@ -1065,6 +1113,7 @@ def _main(args, json_fd):
             if cb is not None:
                 result["cub_on_this_gpu"] = cb
             result["ablation_tensor_core_vs_shuffle"] = ablation_leg(torch, tcu, args)
+            result["adjacent_sizes"] = adjacent_sizes_leg(torch, tcu, args, peak_gbs)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
