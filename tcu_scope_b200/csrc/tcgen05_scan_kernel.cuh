@@ -1,5 +1,6 @@
 // Segmented inclusive scan on the fifth-generation tensor cores: tcgen05.mma
-// with the accumulators in tensor memory, for segments of 16 ... 16384 elements.
+// with the accumulators in tensor memory, for segments of 16 ... 16384 elements
+// (16-bit outputs: up to 2^20).
 //
 // The contraction is the one of compute_wmma_segmented_prefixsum_16n / _256n
 // (src/prefixsum/kernel.cuh:86-150,441-506) -- rows of the input times the
@@ -9,8 +10,11 @@
 // group (four K = 16 steps), issued by one thread, both operands read from
 // shared memory, the fp32 result in tensor memory.  A row's total is the last
 // column of its scan; the carries between the rows of a segment are a
-// shuffle scan over those totals (in double), added while the results are on
-// their way from tensor memory to global memory.
+// shuffle scan over those totals (exact hi / lo float pairs), added while the
+// results are on their way from tensor memory to global memory.  A warp reads
+// 32 rows (2048 elements) of a tile; longer segments are spread over several
+// tiles, one quarter of each, so that one warp still meets all rows of "its"
+// segment in order and carries the running total in registers.
 //
 // Exactness is kept the way the mma.sync kernels keep it (split_hi_lo): four
 // warps split every tile into an exact "hi" tile and an exact "lo" tile in
