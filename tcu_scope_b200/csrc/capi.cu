@@ -297,12 +297,12 @@ bool make_output_tensor_map(CUtensorMap* map, void* d_out, size_t num_elems, boo
              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int LOG2S, bool OUT32>
+template <int LOG2S, bool OUT32, bool kExcl = false>
 cudaError_t launch_tcgen05_scan(const ScanParams& p, const CUtensorMap& omap, int grid, cudaStream_t st) {
   static bool configured[kMaxDevices];
-  cudaError_t e = ensure_smem(tcgen05_scan_kernel<LOG2S, OUT32>, configured, kUscanDynSmemBytes);
+  cudaError_t e = ensure_smem(tcgen05_scan_kernel<LOG2S, OUT32, kExcl>, configured, kUscanDynSmemBytes);
   if (e != cudaSuccess) return e;
-  tcgen05_scan_kernel<LOG2S, OUT32><<<grid, kUscanThreads, kUscanDynSmemBytes, st>>>(p, omap);
+  tcgen05_scan_kernel<LOG2S, OUT32, kExcl><<<grid, kUscanThreads, kUscanDynSmemBytes, st>>>(p, omap);
   return cudaGetLastError();
 }
 
@@ -504,7 +504,8 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   // fp32: 68.6 against 72.6 us; at 2^25 the mma.sync kernels win 20.7 ... 25.6 against 27 us).
   const bool umma_class = f32 ? sc == 4 : (sc == 4 || (sc >= 8 && sc <= 14));
   const size_t umma_from = (!f32 && sc >= 12) ? size_t(1) << 25 : size_t(1) << 26;
-  const bool umma_auto = algo == TCU_ALGO_AUTO && !exclusive && n % kSwizzleRowElems == 0 &&
+  // (exclusive scans: the 16-bit classes only)
+  const bool umma_auto = algo == TCU_ALGO_AUTO && !(exclusive && f32) && n % kSwizzleRowElems == 0 &&
                          n >= umma_from && umma_class;
   if ((algo == TCU_ALGO_TCGEN05 && sc <= 14) || umma_auto) {
     CUtensorMap omap;
@@ -516,6 +517,15 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
       const size_t unit_elems = segment_size > 2048 ? 8 * segment_size : size_t(kUmmaTileElems);
       const size_t units      = (n + unit_elems - 1) / unit_elems;
       const int ugrid         = units < size_t(sms) ? int(units) : sms;
+      if (exclusive) {
+        switch (sc) {
+#define X(C) case C: e = launch_tcgen05_scan<C, false, true>(p, omap, ugrid, st); break;
+          X(4) X(8) X(9) X(10) X(11) X(12) X(13) X(14)
+#undef X
+          default: return TCU_ERR_UNSUPPORTED;
+        }
+        return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+      }
       switch (sc) {
 #define X(C)                                                                              \
   case C:                                                                                 \
@@ -633,7 +643,7 @@ int tcu_segmented_exclusive_scan_f16(const void* d_in, void* d_out, int out_type
                                      size_t workspace_bytes, void* stream) {
   const int sc = segment_class(segment_size);
   if (sc < 0) return TCU_ERR_UNSUPPORTED;
-  return scan_impl(d_in, d_out, out_type, num_segments, segment_size, sc, nullptr, 0, TCU_ALGO_MMA,
+  return scan_impl(d_in, d_out, out_type, num_segments, segment_size, sc, nullptr, 0, TCU_ALGO_AUTO,
                    d_workspace, workspace_bytes, static_cast<cudaStream_t>(stream), true);
 }
 

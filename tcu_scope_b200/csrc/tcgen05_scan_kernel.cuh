@@ -113,7 +113,10 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, int c0, in
 
 // Registers are per SM sub-partition (16 K): 14 warps put four on one, so a thread may use 128
 // at most.  A bound of 512 threads makes the compiler keep to exactly that.
-template <int LOG2S, bool OUT32>
+// kExcl: exclusive scan.  Segments shorter than a row: U is strictly triangular; longer ones: U
+// stays inclusive (its last column is the row total the carries need) and every thread shifts its
+// row by one column on the way out -- column 0 is the carry alone.
+template <int LOG2S, bool OUT32, bool kExcl = false>
 __global__ void __launch_bounds__(512, 1)
     tcgen05_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap omap) {
   static_assert(LOG2S >= 4 && LOG2S <= kUscanMaxLog2, "16 ... 2^20 elements per segment");
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(512, 1)
   // U restricted to the segments inside a row: B[n][k] = 1 iff k <= n and both in one segment.
   for (int idx = threadIdx.x; idx < kUscanN * kSwizzleRowElems; idx += kUscanThreads) {
     const int n = idx / kSwizzleRowElems, k = idx % kSwizzleRowElems;
-    const bool one = k <= n && (S >= 64 || (k >> LOG2S) == (n >> LOG2S));
+    const bool one = (kExcl && S < 64 ? k < n : k <= n) && (S >= 64 || (k >> LOG2S) == (n >> LOG2S));
     *reinterpret_cast<uint16_t*>(bmat + swizzle128(n * 128 + k * 2)) =
         one ? static_cast<uint16_t>(kOne16) : uint16_t(0);
   }
@@ -402,6 +405,8 @@ __global__ void __launch_bounds__(512, 1)
       // 128-byte pieces measured 0.86 of the copy bandwidth where the mma.sync kernels reach 0.97.
       const unsigned long long row0 = quarter_row(i, quarter);  // first row of this warp
       uint8_t* const bufs = stage + (set * 4 + quarter) * 2 * kUscanStageBytes;
+      constexpr bool kShift = kExcl && S >= 64;
+      uint32_t ph = 0u, pl = 0u;  // exclusive: the column before the one being written (bits of 0.f at first)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         if (half == 1) {
@@ -426,10 +431,18 @@ __global__ void __launch_bounds__(512, 1)
           float o[16];
 #pragma unroll
           for (int e = 0; e < 16; e += 2) {  // two outputs per packed fp32x2 instruction
-            const float2 t = add2(add2(make_float2(__uint_as_float(vh[cc][e]), __uint_as_float(vh[cc][e + 1])), cb2),
-                                  add2(make_float2(__uint_as_float(vl[cc][e]), __uint_as_float(vl[cc][e + 1])), cs2));
+            const uint32_t h0 = kShift ? (e == 0 ? ph : vh[cc][e == 0 ? 0 : e - 1]) : vh[cc][e];
+            const uint32_t l0 = kShift ? (e == 0 ? pl : vl[cc][e == 0 ? 0 : e - 1]) : vl[cc][e];
+            const uint32_t h1 = kShift ? vh[cc][e] : vh[cc][e + 1];
+            const uint32_t l1 = kShift ? vl[cc][e] : vl[cc][e + 1];
+            const float2 t = add2(add2(make_float2(__uint_as_float(h0), __uint_as_float(h1)), cb2),
+                                  add2(make_float2(__uint_as_float(l0), __uint_as_float(l1)), cs2));
             o[e]     = t.x;  // (hi + cb) + (lo + cs): two exact sums, one rounding
             o[e + 1] = t.y;
+          }
+          if constexpr (kShift) {
+            ph = vh[cc][15];
+            pl = vl[cc][15];
           }
           if constexpr (S > 2048) {
             if (any_big) {  // warp-uniform: only carries of 2^11 and more are held back

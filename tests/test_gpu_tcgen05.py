@@ -139,3 +139,21 @@ def test_tcgen05_scan_of_long_segments_with_16bit_outputs(s):
         pos = tcu.fill(torch.empty(4 * s, dtype=torch.float16, device="cuda"), 6, 0, "uniform_01")
         got = tcu.segmented_scan(pos, s, out_dtype=torch.float16, algo="tcgen05")
         assert oracle.np_check_f16(bits(got), oracle.c_segmented_scan(bits(pos), s), 2)[0] == 0
+
+
+@pytest.mark.parametrize("s", [16, 256, 2048, 4096, 16384])
+def test_auto_runs_the_tcgen05_scan_for_large_exclusive_scans(s):
+    """Exclusive scans with 16-bit outputs take the tensor-memory kernel on large arrays: a strictly
+    triangular U inside a row for 16-element segments, rows shifted by one column above."""
+    import tcu_scope_b200 as tcu
+    n = (1 << 26) + 64 * s  # not a whole number of work units for the long segments
+    x = tcu.fill(torch.empty(n, dtype=torch.float16, device="cuda"), 321 + s, 0)
+    buf = torch.full((n + 128,), -777.0, dtype=torch.float16, device="cuda")
+    out = buf[64:64 + n]
+    tcu.segmented_scan(x, s, out=out, exclusive=True)
+    ref = oracle.c_segmented_scan(bits(x), s) - bits(x).view(np.float16).astype(np.float64)
+    bad, worst = oracle.np_check_f16(bits(out), ref, 2)
+    assert bad == 0 and worst <= 1, (s, worst)
+    guards = torch.cat([buf[:64], buf[64 + n:]]).float().cpu()
+    assert torch.all(guards == -777.0)
+    assert tcu.device_error() == 0
