@@ -102,6 +102,18 @@ def test_tcgen05_scan_bf16(s, out_dtype):
     assert tcu.device_error() == 0
 
 
+@pytest.mark.parametrize("s", [16, 4096])
+def test_large_exclusive_scan_bf16(s):
+    """Large exclusive scans with 16-bit outputs run the tensor-memory kernel by default."""
+    import tcu_scope_b200 as tcu
+    n = 1 << 26
+    x = tcu.fill(torch.empty(n, dtype=BF, device="cuda"), 600 + s, 0)
+    out = tcu.segmented_scan(x, s, out_dtype=BF, exclusive=True)
+    ref = oracle.np_segmented_scan(bits(x), s, fmt="bf16") - oracle._as_f64(bits(x), "bf16")
+    check(out, ref)
+    assert tcu.device_error() == 0
+
+
 def test_exact_cases_bf16():
     import tcu_scope_b200 as tcu
     ones = torch.ones(1 << 16, dtype=BF, device="cuda")
