@@ -380,7 +380,12 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
                                      out_type == TCU_OUT_F32, false);
     const size_t ctas = ((num_segments + 15) / 16 + kGeneralThreads / 32 - 1) / (kGeneralThreads / 32);
     const size_t cap  = size_t(sms) * 8;
-    e = launch_pdl(seg_rowsum_kernel, r, int(ctas < cap ? ctas : cap), kGeneralThreads, 0, st);
+    const int rgrid   = int(ctas < cap ? ctas : cap);
+    const size_t steps = (segment_size * 2 + 63) / 64;  // 64-byte steps that cover a segment
+    e = steps <= 1   ? launch_pdl(seg_rowsum_kernel<1>, r, rgrid, kGeneralThreads, 0, st)
+        : steps == 2 ? launch_pdl(seg_rowsum_kernel<2>, r, rgrid, kGeneralThreads, 0, st)
+        : steps == 3 ? launch_pdl(seg_rowsum_kernel<3>, r, rgrid, kGeneralThreads, 0, st)
+                     : launch_pdl(seg_rowsum_kernel<4>, r, rgrid, kGeneralThreads, 0, st);
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
   if (sc == kClassGeneral) {

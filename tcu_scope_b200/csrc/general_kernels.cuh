@@ -376,6 +376,11 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsPar
 // for a sum, so a lane loads 16 consecutive bytes of "its" two segments per step (four lanes
 // cover 64 bytes of a segment, the warp whole 32-byte sectors of one contiguous range) and the
 // four registers feed two all-ones MMAs: the row sums come out complete, no shuffles.
+// kR = 64-byte steps per round (loads in flight per lane: 2 kR), the smallest that covers a
+// segment, at most 4: measured at 2^28 elements with kR = 1 / 2 / 3 / 4, 48 elements per segment
+// 0.66 / 0.76 / 0.62 / 0.47 of the copy bandwidth, 80 elements 0.76 / 0.73 / 0.90 / 0.73, 1000
+// elements 0.68 / 0.84 / 0.85 / 0.87.
+template <int kR>
 __global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsParams p) {
   pdl_prologue();
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -387,16 +392,16 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsP
   const Acc zero{0.f, 0.f, 0.f, 0.f};
   const bool f32 = p.out_is_f32 != 0;
 
-  // One round = 128 bytes of each of a group's segments: four loads per lane.  The loads of the
+  // One round = 64 kR bytes of each of a group's segments: 2 kR loads per lane.  The loads of the
   // next round (of this group or of the warp's next group) are issued before the current round
   // is worked on.
-  auto load_round = [&](unsigned long long grp, unsigned int b, uint4 (&x)[2], uint4 (&y)[2]) {
+  auto load_round = [&](unsigned long long grp, unsigned int b, uint4 (&x)[kR], uint4 (&y)[kR]) {
     const unsigned long long seg_lo = grp * 16 + g;
     const bool ok_lo = seg_lo < p.num_segments, ok_hi = seg_lo + 8 < p.num_segments;
     const uint8_t* src_lo = p.in + seg_lo * seg_bytes + 16u * t + b;
     const uint8_t* src_hi = src_lo + 8ull * seg_bytes;
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < kR; ++k) {
       const bool in = b + 64u * k + 16u * t < seg_bytes;
       x[k] = ok_lo && in ? ldg128(src_lo + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
       y[k] = ok_hi && in ? ldg128(src_hi + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
@@ -405,21 +410,21 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsP
   unsigned long long grp = first;
   unsigned int b = 0;
   if (grp >= groups) return;
-  uint4 x[2], y[2];
+  uint4 x[kR], y[kR];
   load_round(grp, b, x, y);
   Acc ah = zero, al = zero;
   for (;;) {
     unsigned long long ngrp = grp;
-    unsigned int nb = b + 128u;
+    unsigned int nb = b + 64u * kR;
     if (nb >= seg_bytes) {
       nb   = 0u;
       ngrp = grp + warps;
     }
     const bool more = ngrp < groups;
-    uint4 nx[2], ny[2];
+    uint4 nx[kR], ny[kR];
     if (more) load_round(ngrp, nb, nx, ny);
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < kR; ++k) {
       uint4 xh, xl, yh, yl;
       split_hi_lo(x[k].x, xh.x, xl.x);
       split_hi_lo(x[k].y, xh.y, xl.y);
@@ -450,7 +455,7 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsP
     }
     if (!more) break;
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < kR; ++k) {
       x[k] = nx[k];
       y[k] = ny[k];
     }
