@@ -494,9 +494,12 @@ int scan_impl(const void* d_in, void* d_out, int out_type, size_t num_segments,
   if (sc == kClassGeneral) {
     const int ggrid = general_grid(num_segments, sms);
     const bool vec  = segment_size % 4 == 0;
+    const bool deep = segment_size >= 32768;  // few, long segments: three steps of loads in flight
     void (*kernel)(ScanParams, unsigned long long) =
-        f32 ? (vec ? seg_scan_general_kernel<true, true> : seg_scan_general_kernel<true, false>)
-            : (vec ? seg_scan_general_kernel<false, true> : seg_scan_general_kernel<false, false>);
+        deep ? (f32 ? (vec ? seg_scan_general_kernel<true, true, 3> : seg_scan_general_kernel<true, false, 3>)
+                    : (vec ? seg_scan_general_kernel<false, true, 3> : seg_scan_general_kernel<false, false, 3>))
+             : (f32 ? (vec ? seg_scan_general_kernel<true, true> : seg_scan_general_kernel<true, false>)
+                    : (vec ? seg_scan_general_kernel<false, true> : seg_scan_general_kernel<false, false>));
     e = launch_pdl(kernel, p, (unsigned long long)segment_size, ggrid, kGeneralThreads, 0, st);
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
