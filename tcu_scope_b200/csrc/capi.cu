@@ -418,8 +418,23 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
     }
     return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
   }
+  p.spread_slices = sc >= 12 && sc <= 14 ? 1u << (sc - 11) : 0u;
   if (sc == kClassLong) {
     if (!ws || ws_bytes < reduce_long_ws_bytes() || !aligned16(ws)) return TCU_ERR_WORKSPACE;
+    // Many long segments: eight segments per work unit, one warp per segment, like the 4096 ...
+    // 16384-element classes (1.0 of the copy bandwidth at 2^28 elements against 0.81 for the
+    // contiguous runs below, whose 148 streams lie megabytes apart).  Taken when the units fill
+    // the SMs evenly; the workspace is then left untouched.
+    if (num_segments > 1 && segment_size / kSliceElems <= (size_t(1) << 20)) {
+      const size_t lunits = (num_segments + 7) / 8;
+      const size_t rounds = (lunits + size_t(sms) - 1) / size_t(sms);
+      if (lunits * 100 >= rounds * size_t(sms) * 85) {
+        p.spread_slices = unsigned(segment_size / kSliceElems);
+        const int sgrid = lunits < size_t(sms) ? int(lunits) : sms;
+        e = (algo == TCU_ALGO_SHUFFLE) ? launch_shuffle_reduce<14>(p, sgrid, st) : launch_reduce<14>(p, sgrid, st);
+        return e == cudaSuccess ? TCU_OK : TCU_ERR_CUDA;
+      }
+    }
     if (grid > kMaxLongGrid) grid = kMaxLongGrid;
     uint8_t* w          = static_cast<uint8_t*>(ws);
     p.done_counter      = reinterpret_cast<unsigned int*>(w);

@@ -33,6 +33,7 @@ struct ReduceParams {
   long long* bound_seg;                  // [2 * gridDim.x] their segment, -1 = none
   unsigned int* done_counter;            // zeroed by the host before the launch
   double* out_f64;                       // optional: segment sums in double (may be null)
+  unsigned int spread_slices;            // classes 12 ... 14: slices (2048 elements) per segment
   unsigned long long test_skip_tile;     // ~0 in production; a test names a tile that is never loaded
 };
 
@@ -246,7 +247,9 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
   // another warp's sum (one barrier of the consumer warps per tile measured 1.01 / 0.97 / 0.95
   // of the copy bandwidth at 4096 / 8192 / 16384 elements, a collector warp 0.93).
   constexpr bool kSpread = SC >= 12 && SC <= 14;
-  constexpr int G        = kSpread ? 1 << (SC - 11) : 1;
+  // (2, 4 or 8 for segments of 4096 ... 16384 elements; longer powers of two are routed through
+  // class 14 with their own count when there are enough segments to fill the SMs this way)
+  const int G = kSpread ? (int)p.spread_slices : 1;
   const unsigned long long num_units = (p.num_segments + kConsumerWarps - 1) / kConsumerWarps;
 
   if (threadIdx.x == 0) {
