@@ -422,9 +422,10 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   if (sc == kClassLong) {
     if (!ws || ws_bytes < reduce_long_ws_bytes() || !aligned16(ws)) return TCU_ERR_WORKSPACE;
     // Many long segments: eight segments per work unit, one warp per segment, like the 4096 ...
-    // 16384-element classes (1.0 of the copy bandwidth at 2^28 elements against 0.81 for the
-    // contiguous runs below, whose 148 streams lie megabytes apart).  Taken when the units fill
-    // the SMs evenly; the workspace is then left untouched.
+    // 16384-element classes (0.94 of the copy bandwidth at 2^28 elements and 32768 per segment
+    // against 0.81 for the kernel below, which pays about 10 us per call for its scratch header,
+    // its flushes and the last CTA's walk).  Taken when the units fill the SMs evenly; the
+    // workspace is then left untouched.
     if (num_segments > 1 && segment_size / kSliceElems <= (size_t(1) << 20)) {
       const size_t lunits = (num_segments + 7) / 8;
       const size_t rounds = (lunits + size_t(sms) - 1) / size_t(sms);
