@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
     if (s_is_last) {
       __threadfence();
       // Stage the 2 * gridDim.x boundary records in the (now idle) ring with
-      // all threads, then let one thread walk them in CTA order.
+      // all threads, then add up each segment's records in CTA order.
       double* sh_val       = reinterpret_cast<double*>(ring);
       long long* sh_seg    = reinterpret_cast<long long*>(ring + 16384);
       const unsigned int n = 2 * gridDim.x;  // the host keeps gridDim.x <= 1024
@@ -472,26 +472,30 @@ __global__ void __launch_bounds__(kThreads, 1) seg_reduce_kernel(const ReducePar
           store_seg(p.out, p.out_is_f32 != 0, 0, (float)total);
           if (p.out_f64) p.out_f64[0] = total;
         }
-      } else if (threadIdx.x == 0) {
-        long long cur_seg  = -1;
-        double cur         = 0.0;
+      } else {
+        // The records are in CTA order, so those of one segment are neighbours (with empty ones,
+        // seg < 0, in between).  The first record of each segment adds up its group, in order:
+        // as many threads at work as there are segments among the records, and a fixed order of
+        // additions whatever that number is.
         const bool out_f32 = p.out_is_f32 != 0;
-        for (unsigned int k = 0; k < n; ++k) {
+        for (unsigned int k = threadIdx.x; k < n; k += kThreads) {
           const long long seg = sh_seg[k];
           if (seg < 0) continue;
-          if (seg != cur_seg) {
-            if (cur_seg >= 0) {
-              store_seg(p.out, out_f32, cur_seg, (float)cur);
-              if (p.out_f64) p.out_f64[cur_seg] = cur;
-            }
-            cur_seg = seg;
-            cur     = 0.0;
+          bool first = true;  // no earlier record of this segment?
+          for (unsigned int j = k; j-- > 0;) {
+            if (sh_seg[j] < 0) continue;
+            first = sh_seg[j] != seg;
+            break;
           }
-          cur += sh_val[k];
-        }
-        if (cur_seg >= 0) {
-          store_seg(p.out, out_f32, cur_seg, (float)cur);
-          if (p.out_f64) p.out_f64[cur_seg] = cur;
+          if (!first) continue;
+          double total = sh_val[k];
+          for (unsigned int j = k + 1; j < n; ++j) {
+            if (sh_seg[j] < 0) continue;
+            if (sh_seg[j] != seg) break;
+            total += sh_val[j];
+          }
+          store_seg(p.out, out_f32, seg, (float)total);
+          if (p.out_f64) p.out_f64[seg] = total;
         }
       }
     }
