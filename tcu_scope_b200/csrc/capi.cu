@@ -422,14 +422,15 @@ int reduce_impl(const void* d_in, void* d_out, double* d_out_f64, int out_type,
   if (sc == kClassLong) {
     if (!ws || ws_bytes < reduce_long_ws_bytes() || !aligned16(ws)) return TCU_ERR_WORKSPACE;
     // Many long segments: eight segments per work unit, one warp per segment, like the 4096 ...
-    // 16384-element classes (0.94 of the copy bandwidth at 2^28 elements and 32768 per segment
-    // against 0.81 for the kernel below, which pays about 10 us per call for its scratch header,
-    // its flushes and the last CTA's walk).  Taken when the units fill the SMs evenly; the
-    // workspace is then left untouched.
+    // 16384-element classes.  Taken when the units fill the SMs evenly -- one round on 85 % of the
+    // SMs or more, or several rounds with the last one at least 95 % full: measured at 2^28
+    // elements, 2^15 / 2^16 / 2^18 elements per segment (1024 / 512 / 128 units), 0.94 / 0.86 /
+    // 0.95 of the copy bandwidth against 0.88 / 0.91 / 0.92 for the kernel below.  The workspace
+    // is then left untouched.
     if (num_segments > 1 && segment_size / kSliceElems <= (size_t(1) << 20)) {
       const size_t lunits = (num_segments + 7) / 8;
       const size_t rounds = (lunits + size_t(sms) - 1) / size_t(sms);
-      if (lunits * 100 >= rounds * size_t(sms) * 85) {
+      if (lunits * 100 >= rounds * size_t(sms) * (rounds == 1 ? 85 : 95)) {
         p.spread_slices = unsigned(segment_size / kSliceElems);
         const int sgrid = lunits < size_t(sms) ? int(lunits) : sms;
         e = (algo == TCU_ALGO_SHUFFLE) ? launch_shuffle_reduce<14>(p, sgrid, st) : launch_reduce<14>(p, sgrid, st);
