@@ -386,7 +386,18 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rows_kernel(const RowsPar
 // segment, at most 4: measured at 2^28 elements with kR = 1 / 2 / 3 / 4, 48 elements per segment
 // 0.66 / 0.76 / 0.62 / 0.47 of the copy bandwidth, 80 elements 0.76 / 0.73 / 0.90 / 0.73, 1000
 // elements 0.68 / 0.84 / 0.85 / 0.87.
-template <int kR>
+// kAny: segments of any number of elements, so a row starts at any even byte address.  A lane
+// then loads the aligned 16 bytes around "its" piece and clears the halves that belong to the
+// neighbouring segments (a sum does not care where in the vector an element sits).
+__device__ __forceinline__ uint4 keep_halves(uint4 v, int i0, unsigned int count) {
+  // halves i0 ... i0 + 7 of the row are in v: keep those with 0 <= index < count
+  auto mask = [&](int i) -> uint32_t {
+    return ((unsigned)i < count ? 0x0000ffffu : 0u) | ((unsigned)(i + 1) < count ? 0xffff0000u : 0u);
+  };
+  return make_uint4(v.x & mask(i0), v.y & mask(i0 + 2), v.z & mask(i0 + 4), v.w & mask(i0 + 6));
+}
+
+template <int kR, bool kAny = false>
 __global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsParams p) {
   pdl_prologue();
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -404,13 +415,30 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsP
   auto load_round = [&](unsigned long long grp, unsigned int b, uint4 (&x)[kR], uint4 (&y)[kR]) {
     const unsigned long long seg_lo = grp * 16 + g;
     const bool ok_lo = seg_lo < p.num_segments, ok_hi = seg_lo + 8 < p.num_segments;
-    const uint8_t* src_lo = p.in + seg_lo * seg_bytes + 16u * t + b;
-    const uint8_t* src_hi = src_lo + 8ull * seg_bytes;
+    if constexpr (kAny) {
+      const unsigned long long a_lo = seg_lo * seg_bytes, a_hi = a_lo + 8ull * seg_bytes;
+      const unsigned int off_lo = (unsigned int)a_lo & 15u, off_hi = (unsigned int)a_hi & 15u;
+      const uint8_t* src_lo = p.in + (a_lo - off_lo) + 16u * t + b;  // 16-byte aligned
+      const uint8_t* src_hi = p.in + (a_hi - off_hi) + 16u * t + b;
+      const unsigned int count = seg_bytes / 2;
 #pragma unroll
-    for (int k = 0; k < kR; ++k) {
-      const bool in = b + 64u * k + 16u * t < seg_bytes;
-      x[k] = ok_lo && in ? ldg128(src_lo + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
-      y[k] = ok_hi && in ? ldg128(src_hi + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
+      for (int k = 0; k < kR; ++k) {
+        const int piece = (int)(b + 64u * k + 16u * t);  // byte offset from the aligned row start
+        const int i_lo = (piece - (int)off_lo) / 2, i_hi = (piece - (int)off_hi) / 2;  // even numerators
+        const bool in_lo = ok_lo && i_lo < (int)count && i_lo + 8 > 0;
+        const bool in_hi = ok_hi && i_hi < (int)count && i_hi + 8 > 0;
+        x[k] = in_lo ? keep_halves(ldg128(src_lo + 64u * k), i_lo, count) : make_uint4(0u, 0u, 0u, 0u);
+        y[k] = in_hi ? keep_halves(ldg128(src_hi + 64u * k), i_hi, count) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    } else {
+      const uint8_t* src_lo = p.in + seg_lo * seg_bytes + 16u * t + b;
+      const uint8_t* src_hi = src_lo + 8ull * seg_bytes;
+#pragma unroll
+      for (int k = 0; k < kR; ++k) {
+        const bool in = b + 64u * k + 16u * t < seg_bytes;
+        x[k] = ok_lo && in ? ldg128(src_lo + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
+        y[k] = ok_hi && in ? ldg128(src_hi + 64u * k) : make_uint4(0u, 0u, 0u, 0u);
+      }
     }
   };
   unsigned long long grp = first;
@@ -422,7 +450,7 @@ __global__ void __launch_bounds__(kGeneralThreads) seg_rowsum_kernel(const RowsP
   for (;;) {
     unsigned long long ngrp = grp;
     unsigned int nb = b + 64u * kR;
-    if (nb >= seg_bytes) {
+    if (nb >= seg_bytes + (kAny ? 14u : 0u)) {  // (a row may start up to 14 bytes into its first vector)
       nb   = 0u;
       ngrp = grp + warps;
     }
