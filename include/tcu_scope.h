@@ -79,9 +79,10 @@ typedef enum {
  * reference's dispatch table, seg_wmma_16n.cu:146-172, and of all its
  * benchmarks) run the tiled kernels at HBM speed; the other multiples of 16
  * the reference accepts run kernels that give a warp 16 segments (reduction,
- * also for multiples of 8) or 16 rows of 16 elements (scan) at a time, up to
- * 2048 elements; every other size (tails masked) runs a one-warp-per-segment
- * kernel (TCU_ALGO_AUTO or TCU_ALGO_MMA only).
+ * also for multiples of 8 and for any size up to 255) or 16 rows of 16
+ * elements (scan) at a time, up to 2048 elements; every other size (tails
+ * masked) runs a one-warp-per-segment kernel (TCU_ALGO_AUTO or TCU_ALGO_MMA
+ * only).
  * d_out: num_segments floats or halves.
  * A workspace is needed only when segment_size > 16384.
  */
